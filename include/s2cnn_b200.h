@@ -1,0 +1,153 @@
+/*
+ * s2cnn_b200 - C ABI of the B200-native spectral hot path of s2cnn.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers must be float32, contiguous,
+ * 16-byte aligned and live on the current CUDA device; `stream` is a cudaStream_t passed as void*
+ * (NULL = the legacy default stream).  All functions return 0 on success and a non-zero status
+ * otherwise, with a message available from s2c_last_error() (thread-local).  Nothing is thrown
+ * across the boundary.  Except for the constant tables (built and uploaded on the first call that
+ * needs a given bandwidth on a given device, and kept until s2c_clear_tables()), the library
+ * allocates no device memory: scratch space is passed in by the caller (`workspace`), sized by
+ * the matching *_workspace() query.  Because that first call allocates and copies synchronously,
+ * warm each shape up once before capturing a CUDA graph.
+ *
+ * Layout conventions are the reference's: complex numbers are pairs of floats (re, im) in a
+ * trailing axis of size 2; spectra carry the spectral index first,
+ *   S2    : row l*l + (l+m),                         l < b, |m| <= l           (b*b rows)
+ *   SO(3) : row l(4l*l-1)/3 + (l+m)(2l+1) + (l+n),   l < b, |m|,|n| <= l       (b(4b*b-1)/3 rows)
+ * signals are [batch, beta, alpha(, gamma)] on the SOFT grid with 2b samples per angle.
+ * `nbatch` is the product of all leading (batch, feature) dimensions.
+ *
+ * Each declaration cites the interface of the reference (jonkhler/s2cnn) that it replaces.
+ */
+#ifndef S2CNN_B200_H_
+#define S2CNN_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status / bookkeeping ------------------------------------------------------------------ */
+const char* s2c_last_error(void);
+int s2c_version(void);
+/* Number of kernels this thread has launched through the library (monotonic counter). */
+long s2c_launch_count(void);
+/* Frees the cached tables of every device (replaces nothing in the reference; its lru_caches
+ * are never cleared). */
+void s2c_clear_tables(void);
+/* Per-kernel timing for benchmarks (no counterpart in the reference): between begin and end every
+ * launch is bracketed by a CUDA event pair on its own stream; end() waits for them and writes one
+ * text line per kernel, "<name> <launches> <total_ms>", into buf. */
+void s2c_timing_begin(void);
+int s2c_timing_end(char* buf, size_t buf_bytes);
+/* 1 when the library was built for the GPU, 0 for the host-emulation build used by the tests. */
+int s2c_is_cuda_build(void);
+
+/* ---- host-side float64 generators (replace lie_learn calls) -------------------------------- */
+/* d^l_mn(beta), (2l+1)x(2l+1) row-major, m,n = -l..l.
+ * Replaces lie_learn wigner_d_matrix as called at s2cnn/soft/so3_fft.py:229-230. */
+int s2c_wigner_d(int l, double beta, double* out);
+/* SOFT quadrature weights, 2b values.  Replaces lie_learn S3.quadrature_weights
+ * (s2cnn/soft/so3_fft.py:220, s2cnn/soft/so3_integrate.py:37). */
+int s2c_quadrature_weights(int b, double* out);
+/* Wigner table in the reference's own layout [2b, nspec(nl)] (float32):
+ * s2cnn/soft/so3_fft.py:212-243 (_setup_so3_fft). */
+int s2c_so3_wigner_table(int b, int nl, int weighted, float* out);
+/* [2b, nl*nl]: s2cnn/soft/s2_fft.py:116-147 (_setup_s2_fft). */
+int s2c_s2_wigner_table(int b, int nl, int weighted, float* out);
+/* Fourier matrix of a kernel grid, F[n_grid][b*b][2], grid = n_grid x (beta, alpha) doubles.
+ * Replaces __setup_s2_ft, s2cnn/s2_ft.py:27-50. */
+int s2c_s2_ft_matrix(int b, const double* grid, int n_grid, float* F);
+/* F[n_grid][nspec(b)][2], grid = n_grid x (beta, alpha, gamma).
+ * Replaces __setup_so3_ft, s2cnn/so3_ft.py:27-52. */
+int s2c_so3_ft_matrix(int b, const double* grid, int n_grid, float* F);
+
+/* ---- SO(3) transforms ----------------------------------------------------------------------- */
+/* Recommended scratch size (bytes) for any of the four SO(3) transforms below; any size that
+ * holds at least one batch element works (the batch is processed in chunks). */
+size_t s2c_so3_fft_workspace(long nbatch, int b_in, int b_out);
+size_t s2c_so3_fft_workspace_min(int b_in, int b_out);
+
+/* x [nbatch, 2b_in, 2b_in, 2b_in] real -> out [nspec(b_out), nbatch, 2].
+ * Replaces so3_rfft, s2cnn/soft/so3_fft.py:64-112 (+ kernel so3fft.cu :246-350, REAL_IN). */
+int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                 void* workspace, size_t workspace_bytes, void* stream);
+/* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].
+ * Replaces so3_fft, s2cnn/soft/so3_fft.py:12-61. */
+int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                void* workspace, size_t workspace_bytes, void* stream);
+/* x [nspec(b_in), nbatch, 2] -> out [nbatch, 2b_out, 2b_out, 2b_out] real: the real part of the
+ * full complex synthesis for ANY spectrum (the reference's CPU semantics, so3_fft.py:184-199).
+ * `bias` (optional, [nfeature]) is added to every sample of row z with feature z % nfeature - the
+ * "+ bias" of s2cnn/soft/s2_conv.py:45 and so3_conv.py:56 fused into the last pass.
+ * Replaces so3_rifft, s2cnn/soft/so3_fft.py:158-202 (+ kernel so3ifft.cu :353-443, REAL_OUT). */
+int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                  const float* bias, int nfeature, void* workspace, size_t workspace_bytes,
+                  void* stream);
+/* x [nspec(b_in), nbatch, 2] -> out [nbatch, 2b_out, 2b_out, 2b_out, 2] complex.
+ * Replaces so3_ifft, s2cnn/soft/so3_fft.py:115-155. */
+int s2c_so3_ifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- S2 transforms -------------------------------------------------------------------------- */
+size_t s2c_s2_fft_workspace(long nbatch, int b_in, int b_out);
+/* x [nbatch, 2b_in, 2b_in(, 2)] (real when x_is_real, else complex) -> out [b_out^2, nbatch, 2];
+ * requires b_out <= b_in.  Replaces s2_fft and S2_fft_real.forward,
+ * s2cnn/soft/s2_fft.py:13-58,226-232 (+ kernel s2fft.cu :151-185). */
+int s2c_s2_fft(const float* x, int x_is_real, float* out, long nbatch, int b_in, int b_out,
+               int for_grad, void* workspace, size_t workspace_bytes, void* stream);
+/* x [b_in^2, nbatch, 2] -> out [nbatch, 2b_out, 2b_out(, 2)] (real part only when out_is_real);
+ * requires b_out >= b_in.  Replaces s2_ifft and S2_ifft_real.forward,
+ * s2cnn/soft/s2_fft.py:61-106,239-245 (+ kernel s2ifft.cu :188-223). */
+int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_in, int b_out,
+                int for_grad, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- spectral products ---------------------------------------------------------------------- */
+/* z[l,m,n,i,j] = sum_{p,k} x[l,m,p,i,k] conj(y[l,n,p,k,j]);  x [nspec(nl), nbatch, f_in, 2],
+ * y [nspec(nl), f_in, f_out, 2], z [nspec(nl), nbatch, f_out, 2].
+ * Replaces so3_mm / _cuda_SO3_mm.forward, s2cnn/so3_mm.py:8-93. */
+int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nbatch, int f_in, int f_out,
+               void* stream);
+/* gx = d/dx: replaces _cuda_SO3_mm.backward (grad-x instantiation), s2cnn/so3_mm.py:108-113. */
+int s2c_so3_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nbatch, int f_in,
+                     int f_out, void* stream);
+/* gy = d/dy: replaces _cuda_SO3_mm.backward (grad-y instantiation), s2cnn/so3_mm.py:115-120. */
+int s2c_so3_mm_grady(const float* gz, const float* x, float* gy, int nl, int nbatch, int f_in,
+                     int f_out, void* stream);
+/* z[l,m,n,i,j] = sum_k x[l,m,i,k] conj(y[l,n,k,j]);  x [nl^2, nbatch, f_in, 2],
+ * y [nl^2, f_in, f_out, 2], z [nspec(nl), nbatch, f_out, 2].
+ * Replaces s2_mm / _cuda_s2_mm, s2cnn/s2_mm.py:10-28,104-137 (+ kernel s2mm.cu :140-198). */
+int s2c_s2_mm(const float* x, const float* y, float* z, int nl, int nbatch, int f_in, int f_out,
+              void* stream);
+/* Replaces _cuda_S2_mm.backward grad-x, s2cnn/s2_mm.py:85-92 (+ s2mm_gradx.cu :201-255). */
+int s2c_s2_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nbatch, int f_in,
+                    int f_out, void* stream);
+/* Replaces _cuda_S2_mm.backward grad-y, s2cnn/s2_mm.py:94-99 (+ s2mm_grady.cu :258-312). */
+int s2c_s2_mm_grady(const float* gz, const float* x, float* gy, int nl, int nbatch, int f_in,
+                    int f_out, void* stream);
+
+/* ---- kernel-grid -> spectrum transforms ----------------------------------------------------- */
+/* out[s, f, :] = sum_a x[f, a] F[a, s, :];  x [nf, n_grid], F [n_grid, nspec, 2] (device),
+ * out [nspec, nf, 2].  Replaces the einsum of s2_rft / so3_rft, s2cnn/s2_ft.py:22,
+ * s2cnn/so3_ft.py:22. */
+int s2c_rft_forward(const float* x, const float* F, float* out, int nf, int n_grid, int nspec,
+                    void* stream);
+/* gx[f, a] = sum_{s,c} g[s, f, c] F[a, s, c]: the autograd transpose of the einsum above. */
+int s2c_rft_backward(const float* g, const float* F, float* gx, int nf, int n_grid, int nspec,
+                     void* stream);
+
+/* ---- integration ---------------------------------------------------------------------------- */
+/* out[z] = sum_beta w_beta sum_{alpha,gamma} x[z, beta, alpha, gamma]; x [n, 2b, 2b, 2b].
+ * With relu != 0 the integrand is max(x, 0) (activation fused into the read).
+ * Replaces so3_integrate, s2cnn/soft/so3_integrate.py:7-29. */
+int s2c_so3_integrate(const float* x, float* out, long n, int b, int relu, void* stream);
+/* gx[z, beta, :, :] = g[z] w_beta (masked by x > 0 when relu != 0; x may be NULL otherwise). */
+int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n, int b, int relu,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* S2CNN_B200_H_ */

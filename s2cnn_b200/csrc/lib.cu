@@ -1,0 +1,536 @@
+// C-ABI entry points of s2cnn_b200 (see include/s2cnn_b200.h) and the host-side dispatch that
+// sequences the kernels.  Single translation unit: nvcc -gencode arch=compute_100a,code=sm_100a
+// for the product; g++ -x c++ -DS2C_EMUL for the host-emulation build used by the CPU tests.
+#include "../../include/s2cnn_b200.h"
+
+#include <algorithm>
+#include <complex>
+
+#include "backend.h"
+#include "host_math.h"
+#include "tables.h"
+#include "fft_device.h"
+#include "so3_kernels.h"
+#include "cgemm_kernels.h"
+#include "misc_kernels.h"
+
+namespace s2c {
+thread_local long g_launch_count = 0;
+
+#define S2C_TRY(expr)            \
+  do {                           \
+    int rc__ = (expr);           \
+    if (rc__ != S2C_OK) return rc__; \
+  } while (0)
+
+static inline stream_t as_stream(void* s) { return (stream_t)s; }
+
+static inline int fft_group(int N) { return std::max(1, std::min(256, 4096 / N)); }
+
+static size_t so3_ws_per_z(int N, int K) {
+  // two scratch arrays of complex numbers: [z][K][N][N] and [K][2K-1][z][N]
+  return ((size_t)K * N * N + (size_t)K * (2 * K - 1) * N) * sizeof(float2);
+}
+static size_t s2_ws_per_z(int N, int K) { return (size_t)(2 * K - 1) * N * sizeof(float2); }
+
+static int check_b(int b_in, int b_out) {
+  if (b_in < 1 || b_out < 1) return fail(S2C_ERR_BAD_ARG, "bandwidths must be >= 1");
+  return S2C_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SO(3) analysis:  real signal (strided) -> spectrum rows [nspec(b_out)][nbatch]
+// ---------------------------------------------------------------------------------------------
+static int so3_analysis(const float* x, long in_stride, long in_off, float2* out, long nbatch,
+                        int b_in, int b_out, bool weighted, int mode, void* ws, size_t ws_bytes,
+                        stream_t st) {
+  const int N = 2 * b_in, K = std::min(b_in, b_out);
+  FftDev fft;
+  PanelsDev pan;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b_in, b_out, K, weighted, false, pan));
+  const size_t per_z = so3_ws_per_z(N, K);
+  long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
+  if (chunk < 1 || ws == nullptr)
+    return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" +
+                                       std::to_string(per_z) + " bytes needed)");
+  if (b_out > b_in && mode == kSo3Real)  // rows with |m| or |n| >= b_in stay zero (so3_fft.py:44-48)
+    S2C_TRY(dev_memset_async(out, 0, (size_t)so3_nspec(b_out) * nbatch * sizeof(float2), st));
+  const int G = fft_group(N);
+  const size_t fft_smem = fft_smem_bytes(N, G);
+  for (long z0 = 0; z0 < nbatch; z0 += chunk) {
+    const long zc = std::min(chunk, nbatch - z0);
+    float2* u = (float2*)ws;
+    float2* v = u + (size_t)zc * K * N * N;
+    FwdGammaParams g;
+    g.x = x + (size_t)z0 * N * N * N * in_stride;
+    g.in_stride = in_stride;
+    g.in_off = in_off;
+    g.u = u;
+    g.N = N; g.b = b_in; g.K = K; g.G = G;
+    g.npairs = zc * N * b_in;
+    g.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_fwd_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g));
+    FwdAlphaParams a;
+    a.in = (const float*)u;
+    a.in_real = 0;
+    a.v = v;
+    a.nbatch = (int)zc; a.N = N; a.K = K; a.Kn = K; a.G = G;
+    a.nrows = zc * K * N;
+    a.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_fwd_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem, st, a));
+    FwdWignerParams w;
+    w.v = v;
+    w.out = out + z0;
+    w.out_zstride = nbatch;
+    w.pan = pan;
+    w.nbatch = (int)zc; w.N = N; w.K = K; w.nl = b_out;
+    w.ZT = (int)std::min<long>(32, zc);
+    w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
+    w.mode = mode;
+    const size_t wsm = align_up((size_t)b_out * (N + 1) * sizeof(float), 16) +
+                       (size_t)w.ZT * (N + 1) * sizeof(float2);
+    S2C_TRY(S2C_LAUNCH(so3_fwd_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+  }
+  return S2C_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SO(3) synthesis:  spectrum rows [nspec(b_in)][nbatch] -> real signal (strided)
+// ---------------------------------------------------------------------------------------------
+static int so3_synthesis(const float2* x, float* out, long out_stride, long out_off, long nbatch,
+                         int b_in, int b_out, bool weighted, int mode, const float* bias,
+                         int nfeat, void* ws, size_t ws_bytes, stream_t st) {
+  const int N = 2 * b_out, K = std::min(b_in, b_out);
+  FftDev fft;
+  PanelsDev pan;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b_out, K, K, weighted, false, pan));
+  const size_t per_z = so3_ws_per_z(N, K);
+  long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
+  if (chunk < 1 || ws == nullptr)
+    return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" +
+                                       std::to_string(per_z) + " bytes needed)");
+  const int G = fft_group(N);
+  const size_t fft_smem = fft_smem_bytes(N, G);
+  for (long z0 = 0; z0 < nbatch; z0 += chunk) {
+    const long zc = std::min(chunk, nbatch - z0);
+    float2* t = (float2*)ws;                       // [z][K][N][N]
+    float2* s = t + (size_t)zc * K * N * N;        // [K][2K-1][z][N]
+    InvWignerParams w;
+    w.x = x + z0;
+    w.x_zstride = nbatch;
+    w.s = s;
+    w.pan = pan;
+    w.nbatch = (int)zc; w.N = N; w.K = K;
+    w.ZT = (int)std::min<long>(32, zc);
+    w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
+    w.mode = mode;
+    const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
+    S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+    InvAlphaParams a;
+    a.s = s;
+    a.out = (float*)t;
+    a.out_real = 0;
+    a.herm_n0 = 1;
+    a.nbatch = (int)zc; a.N = N; a.K = K; a.Kn = K; a.G = G;
+    a.nrows = zc * K * N;
+    a.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_inv_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem, st, a));
+    InvGammaParams g;
+    g.t = t;
+    g.out = out + (size_t)z0 * N * N * N * out_stride;
+    g.out_stride = out_stride;
+    g.out_off = out_off;
+    g.bias = bias;
+    g.nfeat = nfeat > 0 ? nfeat : 1;
+    g.z0 = z0;
+    g.N = N; g.b = b_out; g.K = K; g.G = G;
+    g.npairs = zc * N * b_out;
+    g.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_inv_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g));
+  }
+  return S2C_OK;
+}
+
+static int mm_dispatch(bool so3, int op, const float* a, const float* b, float* c, int nl, int nb,
+                       int fi, int fo, stream_t st) {
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+  CgemmParams p = mm_params(so3, op, nl, nb, fi, fo);
+  p.A = (const float2*)a;
+  p.B = (const float2*)b;
+  p.C = (float2*)c;
+  return S2C_LAUNCH(cgemm_grouped, cgemm_total_tiles(p), 256, cgemm_smem_bytes(), st, p);
+}
+
+}  // namespace s2c
+
+using namespace s2c;
+
+extern "C" {
+
+const char* s2c_last_error(void) { return last_error_ref().c_str(); }
+int s2c_version(void) { return 100; }
+long s2c_launch_count(void) { return g_launch_count; }
+void s2c_clear_tables(void) { TableCache::get().clear(); }
+int s2c_is_cuda_build(void) {
+#ifdef S2C_EMUL
+  return 0;
+#else
+  return 1;
+#endif
+}
+
+void s2c_timing_begin(void) {
+#ifndef S2C_EMUL
+  timing_recs().clear();
+  timing_on() = true;
+#endif
+}
+
+int s2c_timing_end(char* buf, size_t buf_bytes) {
+  if (!buf || buf_bytes == 0) return fail(S2C_ERR_BAD_ARG, "s2c_timing_end: no buffer");
+  buf[0] = 0;
+#ifndef S2C_EMUL
+  timing_on() = false;
+  struct Acc { long n = 0; double ms = 0; };
+  std::vector<std::pair<std::string, Acc>> acc;
+  for (auto& r : timing_recs()) {
+    float ms = 0.f;
+    cudaEventSynchronize(r.b);
+    cudaEventElapsedTime(&ms, r.a, r.b);
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+    size_t i = 0;
+    for (; i < acc.size(); ++i) if (acc[i].first == r.name) break;
+    if (i == acc.size()) acc.push_back({r.name, Acc()});
+    acc[i].second.n += 1;
+    acc[i].second.ms += ms;
+  }
+  timing_recs().clear();
+  std::string out;
+  for (auto& kv : acc) {
+    char line[256];
+    std::snprintf(line, sizeof(line), "%s %ld %.6f\n", kv.first.c_str(), kv.second.n, kv.second.ms);
+    out += line;
+  }
+  if (out.size() + 1 > buf_bytes) return fail(S2C_ERR_BAD_ARG, "s2c_timing_end: buffer too small");
+  std::memcpy(buf, out.c_str(), out.size() + 1);
+#endif
+  return S2C_OK;
+}
+
+// ---- host generators ---------------------------------------------------------------------------
+int s2c_wigner_d(int l, double beta, double* out) {
+  if (l < 0 || !out) return fail(S2C_ERR_BAD_ARG, "s2c_wigner_d: bad argument");
+  const int L = 2 * l + 1;
+  std::vector<double> col(l + 2);
+  for (int m = -l; m <= l; ++m)
+    for (int n = -l; n <= l; ++n) {
+      const int l0 = wigner_d_degrees(m, n, beta, l + 1, col.data());
+      out[(m + l) * L + (n + l)] = col[l - l0];
+    }
+  return S2C_OK;
+}
+
+int s2c_quadrature_weights(int b, double* out) {
+  if (b < 1 || !out) return fail(S2C_ERR_BAD_ARG, "s2c_quadrature_weights: bad argument");
+  std::vector<double> w;
+  quadrature_weights(b, w);
+  std::copy(w.begin(), w.end(), out);
+  return S2C_OK;
+}
+
+int s2c_so3_wigner_table(int b, int nl, int weighted, float* out) {
+  if (b < 1 || nl < 1 || !out) return fail(S2C_ERR_BAD_ARG, "s2c_so3_wigner_table: bad argument");
+  std::vector<double> beta, w, col(nl + 1);
+  soft_betas(b, beta);
+  quadrature_weights(b, w);
+  const long ns = so3_nspec(nl);
+  for (int j = 0; j < 2 * b; ++j)
+    for (int m = -(nl - 1); m < nl; ++m)
+      for (int n = -(nl - 1); n < nl; ++n) {
+        const int l0 = wigner_d_degrees(m, n, beta[j], nl, col.data());
+        for (int l = l0; l < nl; ++l)
+          out[j * ns + so3_row(l, m, n)] =
+              (float)(col[l - l0] * (weighted ? w[j] : (2.0 * l + 1.0)));
+      }
+  return S2C_OK;
+}
+
+int s2c_s2_wigner_table(int b, int nl, int weighted, float* out) {
+  if (b < 1 || nl < 1 || !out) return fail(S2C_ERR_BAD_ARG, "s2c_s2_wigner_table: bad argument");
+  std::vector<double> beta, w, col(nl + 1);
+  soft_betas(b, beta);
+  quadrature_weights(b, w);
+  for (int j = 0; j < 2 * b; ++j)
+    for (int m = -(nl - 1); m < nl; ++m) {
+      const int l0 = wigner_d_degrees(m, 0, beta[j], nl, col.data());
+      for (int l = l0; l < nl; ++l)
+        out[(long)j * nl * nl + l * l + l + m] =
+            (float)(col[l - l0] * (weighted ? w[j] * 2.0 * b : (2.0 * l + 1.0)));
+    }
+  return S2C_OK;
+}
+
+// F = conj(D^l_mn(alpha, beta, gamma)) = exp(-i m alpha) d^l_mn(beta) exp(-i n gamma)
+int s2c_so3_ft_matrix(int b, const double* grid, int n_grid, float* F) {
+  if (b < 1 || n_grid < 1 || !grid || !F) return fail(S2C_ERR_BAD_ARG, "s2c_so3_ft_matrix: bad argument");
+  const long ns = so3_nspec(b);
+  std::vector<double> col(b + 1);
+  for (int i = 0; i < n_grid; ++i) {
+    const double beta = grid[3 * i], alpha = grid[3 * i + 1], gamma = grid[3 * i + 2];
+    for (int m = -(b - 1); m < b; ++m)
+      for (int n = -(b - 1); n < b; ++n) {
+        const int l0 = wigner_d_degrees(m, n, beta, b, col.data());
+        const std::complex<double> ph = std::exp(std::complex<double>(0.0, -(m * alpha + n * gamma)));
+        for (int l = l0; l < b; ++l) {
+          const std::complex<double> v = ph * col[l - l0];
+          float* dst = F + ((long)i * ns + so3_row(l, m, n)) * 2;
+          dst[0] = (float)v.real();
+          dst[1] = (float)v.imag();
+        }
+      }
+  }
+  return S2C_OK;
+}
+
+// F = 2b conj(D^l_m0(alpha, beta, 0))
+int s2c_s2_ft_matrix(int b, const double* grid, int n_grid, float* F) {
+  if (b < 1 || n_grid < 1 || !grid || !F) return fail(S2C_ERR_BAD_ARG, "s2c_s2_ft_matrix: bad argument");
+  std::vector<double> col(b + 1);
+  for (int i = 0; i < n_grid; ++i) {
+    const double beta = grid[2 * i], alpha = grid[2 * i + 1];
+    for (int m = -(b - 1); m < b; ++m) {
+      const int l0 = wigner_d_degrees(m, 0, beta, b, col.data());
+      const std::complex<double> ph = std::exp(std::complex<double>(0.0, -m * alpha));
+      for (int l = l0; l < b; ++l) {
+        const std::complex<double> v = (2.0 * b) * ph * col[l - l0];
+        float* dst = F + ((long)i * b * b + l * l + l + m) * 2;
+        dst[0] = (float)v.real();
+        dst[1] = (float)v.imag();
+      }
+    }
+  }
+  return S2C_OK;
+}
+
+// ---- SO(3) transforms ----------------------------------------------------------------------------
+size_t s2c_so3_fft_workspace_min(int b_in, int b_out) {
+  // the beta grid is b_in's for analysis and b_out's for synthesis; take the larger of the two
+  const int K = std::min(b_in, b_out);
+  return std::max(so3_ws_per_z(2 * b_in, K), so3_ws_per_z(2 * b_out, K));
+}
+
+size_t s2c_so3_fft_workspace(long nbatch, int b_in, int b_out) {
+  const size_t per_z = s2c_so3_fft_workspace_min(b_in, b_out);
+  const size_t target = (size_t)256 << 20;
+  long chunk = (long)std::max<size_t>(32, target / per_z);
+  chunk = std::min(chunk, std::max(1L, nbatch));
+  return per_z * (size_t)chunk;
+}
+
+int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                 void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rfft: bad argument");
+  return so3_analysis(x, 1, 0, (float2*)out, nbatch, b_in, b_out, !for_grad, kSo3Real, ws,
+                      ws_bytes, as_stream(stream));
+}
+
+int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_fft: bad argument");
+  // linearity: FT(re + i im) = FT(re) + i FT(im), each a real-input transform
+  S2C_TRY(so3_analysis(x, 2, 0, (float2*)out, nbatch, b_in, b_out, !for_grad, kSo3Real, ws,
+                       ws_bytes, as_stream(stream)));
+  return so3_analysis(x, 2, 1, (float2*)out, nbatch, b_in, b_out, !for_grad, kSo3AccumI, ws,
+                      ws_bytes, as_stream(stream));
+}
+
+int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                  const float* bias, int nfeature, void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft: bad argument");
+  if (bias && nfeature < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft: nfeature must be >= 1 with a bias");
+  return so3_synthesis((const float2*)x, out, 1, 0, nbatch, b_in, b_out, for_grad != 0, kSo3Real,
+                       bias, nfeature, ws, ws_bytes, as_stream(stream));
+}
+
+int s2c_so3_ifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
+                 void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_ifft: bad argument");
+  // Re(A X) and Im(A X) = Re(A (-i X)) for the complex-linear synthesis A
+  S2C_TRY(so3_synthesis((const float2*)x, out, 2, 0, nbatch, b_in, b_out, for_grad != 0, kSo3Real,
+                        nullptr, 1, ws, ws_bytes, as_stream(stream)));
+  return so3_synthesis((const float2*)x, out, 2, 1, nbatch, b_in, b_out, for_grad != 0, kSo3RotI,
+                       nullptr, 1, ws, ws_bytes, as_stream(stream));
+}
+
+// ---- S2 transforms -------------------------------------------------------------------------------
+size_t s2c_s2_fft_workspace(long nbatch, int b_in, int b_out) {
+  const int K = std::min(b_in, b_out), N = 2 * std::max(b_in, b_out);
+  return s2_ws_per_z(N, K) * (size_t)std::max(1L, nbatch);
+}
+
+int s2c_s2_fft(const float* x, int x_is_real, float* out, long nbatch, int b_in, int b_out,
+               int for_grad, void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_s2_fft: bad argument");
+  if (b_out > b_in) return fail(S2C_ERR_BAD_ARG, "s2c_s2_fft: requires b_out <= b_in");
+  stream_t st = as_stream(stream);
+  const int N = 2 * b_in, K = b_out;
+  FftDev fft;
+  PanelsDev pan;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b_in, b_out, K, !for_grad, true, pan));
+  const size_t per_z = s2_ws_per_z(N, K);
+  long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
+  if (chunk < 1 || !ws) return fail(S2C_ERR_WORKSPACE, "s2c_s2_fft: workspace too small");
+  const int G = fft_group(N);
+  for (long z0 = 0; z0 < nbatch; z0 += chunk) {
+    const long zc = std::min(chunk, nbatch - z0);
+    FwdAlphaParams a;
+    a.in = x + (size_t)z0 * N * N * (x_is_real ? 1 : 2);
+    a.in_real = x_is_real ? 1 : 0;
+    a.v = (float2*)ws;
+    a.nbatch = (int)zc; a.N = N; a.K = K; a.Kn = 1; a.G = G;
+    a.nrows = zc * N;
+    a.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_fwd_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem_bytes(N, G), st, a));
+    FwdWignerParams w;
+    w.v = (const float2*)ws;
+    w.out = (float2*)out + z0;
+    w.out_zstride = nbatch;
+    w.pan = pan;
+    w.nbatch = (int)zc; w.N = N; w.K = K; w.nl = b_out;
+    w.ZT = (int)std::min<long>(32, zc);
+    w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
+    w.mode = kS2;
+    const size_t wsm = align_up((size_t)b_out * (N + 1) * sizeof(float), 16) +
+                       (size_t)w.ZT * (N + 1) * sizeof(float2);
+    S2C_TRY(S2C_LAUNCH(so3_fwd_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+  }
+  return S2C_OK;
+}
+
+int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_in, int b_out,
+                int for_grad, void* ws, size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_s2_ifft: bad argument");
+  if (b_out < b_in) return fail(S2C_ERR_BAD_ARG, "s2c_s2_ifft: requires b_out >= b_in");
+  stream_t st = as_stream(stream);
+  const int N = 2 * b_out, K = b_in;
+  FftDev fft;
+  PanelsDev pan;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b_out, b_in, K, for_grad != 0, true, pan));
+  const size_t per_z = s2_ws_per_z(N, K);
+  long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
+  if (chunk < 1 || !ws) return fail(S2C_ERR_WORKSPACE, "s2c_s2_ifft: workspace too small");
+  const int G = fft_group(N);
+  for (long z0 = 0; z0 < nbatch; z0 += chunk) {
+    const long zc = std::min(chunk, nbatch - z0);
+    InvWignerParams w;
+    w.x = (const float2*)x + z0;
+    w.x_zstride = nbatch;
+    w.s = (float2*)ws;
+    w.pan = pan;
+    w.nbatch = (int)zc; w.N = N; w.K = K;
+    w.ZT = (int)std::min<long>(32, zc);
+    w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
+    w.mode = kS2;
+    const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
+    S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+    InvAlphaParams a;
+    a.s = (const float2*)ws;
+    a.out = out + (size_t)z0 * N * N * (out_is_real ? 1 : 2);
+    a.out_real = out_is_real ? 1 : 0;
+    a.herm_n0 = 0;
+    a.nbatch = (int)zc; a.N = N; a.K = K; a.Kn = 1; a.G = G;
+    a.nrows = zc * N;
+    a.fft = fft;
+    S2C_TRY(S2C_LAUNCH(so3_inv_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem_bytes(N, G), st, a));
+  }
+  return S2C_OK;
+}
+
+// ---- spectral products ---------------------------------------------------------------------------
+int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, int fo, void* st) {
+  if (!x || !y || !z) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm: null pointer");
+  return mm_dispatch(true, kMmFwd, x, y, z, nl, nb, fi, fo, as_stream(st));
+}
+int s2c_so3_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nb, int fi, int fo,
+                     void* st) {
+  if (!gz || !y || !gx) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm_gradx: null pointer");
+  return mm_dispatch(true, kMmGradX, gz, y, gx, nl, nb, fi, fo, as_stream(st));
+}
+int s2c_so3_mm_grady(const float* gz, const float* x, float* gy, int nl, int nb, int fi, int fo,
+                     void* st) {
+  if (!gz || !x || !gy) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm_grady: null pointer");
+  return mm_dispatch(true, kMmGradY, x, gz, gy, nl, nb, fi, fo, as_stream(st));
+}
+int s2c_s2_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, int fo, void* st) {
+  if (!x || !y || !z) return fail(S2C_ERR_BAD_ARG, "s2c_s2_mm: null pointer");
+  return mm_dispatch(false, kMmFwd, x, y, z, nl, nb, fi, fo, as_stream(st));
+}
+int s2c_s2_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nb, int fi, int fo,
+                    void* st) {
+  if (!gz || !y || !gx) return fail(S2C_ERR_BAD_ARG, "s2c_s2_mm_gradx: null pointer");
+  return mm_dispatch(false, kMmGradX, gz, y, gx, nl, nb, fi, fo, as_stream(st));
+}
+int s2c_s2_mm_grady(const float* gz, const float* x, float* gy, int nl, int nb, int fi, int fo,
+                    void* st) {
+  if (!gz || !x || !gy) return fail(S2C_ERR_BAD_ARG, "s2c_s2_mm_grady: null pointer");
+  return mm_dispatch(false, kMmGradY, x, gz, gy, nl, nb, fi, fo, as_stream(st));
+}
+
+// ---- kernel-grid -> spectrum -----------------------------------------------------------------------
+int s2c_rft_forward(const float* x, const float* F, float* out, int nf, int ng, int ns, void* st) {
+  if (!x || !F || !out || nf < 1 || ng < 1 || ns < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_rft_forward: bad argument");
+  RftFwdParams p;
+  p.x = x; p.F = (const float2*)F; p.out = (float2*)out;
+  p.nf = nf; p.ng = ng; p.ns = ns;
+  p.tiles_f = (nf + kRftTF - 1) / kRftTF;
+  const long tiles_s = (ns + kRftTS - 1) / kRftTS;
+  const size_t sm = kRftTF * (kRftTA + 1) * 4 + kRftTA * kRftTS * 8;
+  return S2C_LAUNCH(rft_forward, p.tiles_f * tiles_s, 256, sm, as_stream(st), p);
+}
+
+int s2c_rft_backward(const float* g, const float* F, float* gx, int nf, int ng, int ns, void* st) {
+  if (!g || !F || !gx || nf < 1 || ng < 1 || ns < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_rft_backward: bad argument");
+  RftBwdParams p;
+  p.g = (const float2*)g; p.F = (const float2*)F; p.gx = gx;
+  p.nf = nf; p.ng = ng; p.ns = ns;
+  p.tiles_f = (nf + kRftTF - 1) / kRftTF;
+  const long tiles_a = (ng + kRftTA - 1) / kRftTA;
+  const size_t sm = kRftTS * kRftTF * 8 + kRftTA * (kRftTS + 1) * 8;
+  return S2C_LAUNCH(rft_backward, p.tiles_f * tiles_a, 256, sm, as_stream(st), p);
+}
+
+// ---- integration ---------------------------------------------------------------------------------
+int s2c_so3_integrate(const float* x, float* out, long n, int b, int relu, void* st) {
+  if (!x || !out || n < 1 || b < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_integrate: bad argument");
+  IntegrateParams p;
+  p.x = x; p.out = out; p.n = n; p.N = 2 * b; p.relu = relu;
+  S2C_TRY(TableCache::get().quad_weights(b, &p.w));
+  return S2C_LAUNCH(so3_integrate_fwd, n, 256, 256 * sizeof(float), as_stream(st), p);
+}
+
+int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n, int b, int relu,
+                               void* st) {
+  if (!g || !gx || n < 1 || b < 1 || (relu && !x))
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_integrate_backward: bad argument");
+  IntegrateBwdParams p;
+  p.g = g; p.x = x; p.gx = gx; p.N = 2 * b; p.relu = relu;
+  p.total = n * (long)p.N * p.N * p.N;
+  S2C_TRY(TableCache::get().quad_weights(b, &p.w));
+  const long blocks = std::min<long>((p.total + 255) / 256, 148L * 16);
+  return S2C_LAUNCH(so3_integrate_bwd, blocks, 256, 0, as_stream(st), p);
+}
+
+}  // extern "C"

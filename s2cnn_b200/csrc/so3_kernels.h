@@ -1,0 +1,390 @@
+// SO(3) and S2 generalised FFT kernels (general path: any bandwidth, three passes per
+// direction with two scratch arrays in global memory, processed in batch chunks).
+//
+// Replaces the reference's NVRTC kernels so3fft.cu / so3ifft.cu (s2cnn/soft/so3_fft.py:246-443)
+// and s2fft.cu / s2ifft.cu (s2cnn/soft/s2_fft.py:151-223) together with the torch.fft calls
+// around them.  Notation: N = 2b samples per angle; K = number of kept frequencies
+// (|m|, n < K); z = flattened batch index.
+//
+//   analysis :  x[z][beta][alpha][gamma]
+//     fwd_gamma   real rows -> FFT over gamma (two rows per complex transform)
+//                 -> U[z][n][beta][alpha]           (n = 0..K-1, the Hermitian half)
+//     fwd_alpha   rows of U -> FFT over alpha -> V[n][m][z][beta]   (|m| < K)
+//     fwd_wigner  per (m, n):  X[l][z] = sum_beta W[l][beta] V[z][beta], plus the mirrored row
+//                 X[l,-m,-n] = (-1)^(m-n) conj X[l,m,n]  (real input)
+//   synthesis:  the same three passes in reverse (inv_wigner, inv_alpha, inv_gamma).  The
+//     spectrum is first symmetrised, Xs = (X[l,m,n] + (-1)^(m-n) conj X[l,-m,-n]) / 2, which makes
+//     the real-output transform equal to the real part of the full complex transform for ANY
+//     spectrum - the behaviour of the reference's CPU branch (so3_fft.py:184-199).
+//
+// The S2 transforms are the n = 0 special case of the same kernels (mode flags).
+#pragma once
+
+#include "backend.h"
+#include "fft_device.h"
+#include "tables.h"
+
+namespace s2c {
+
+constexpr int kThreads = 256;
+
+S2C_HD size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Shared-memory prologue common to the FFT kernels: twiddles and digit map.
+struct FftSmem {
+  float2* tw;
+  unsigned short* pos;
+  float2* data;
+};
+S2C_D FftSmem fft_smem_carve(unsigned char* smem, int n) {
+  FftSmem s;
+  s.tw = reinterpret_cast<float2*>(smem);
+  s.pos = reinterpret_cast<unsigned short*>(smem + (size_t)n * sizeof(float2));
+  s.data = reinterpret_cast<float2*>(smem + align_up((size_t)n * (sizeof(float2) + 2), 16));
+  return s;
+}
+inline size_t fft_smem_bytes(int n, int rows) {
+  return align_up((size_t)n * (sizeof(float2) + 2), 16) + (size_t)rows * (n + 1) * sizeof(float2);
+}
+S2C_D void fft_smem_load_tables(const Ctx& ctx, const FftSmem& s, const FftDev& f) {
+  for (int i = ctx.tid; i < f.desc.n; i += ctx.nthr) {
+    s.tw[i] = f.tw[i];
+    s.pos[i] = f.pos[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// analysis, pass 1: FFT over gamma of real rows
+// ---------------------------------------------------------------------------------------------
+struct FwdGammaParams {
+  const float* x;     // real signal, element e at x[e * in_stride + in_off]
+  long in_stride, in_off;
+  float2* u;          // [z][n < K][beta][alpha]
+  int N, b, K, G;
+  long npairs;        // nbatch * N * b row pairs; pair id = (z * N + beta) * b + p
+  FftDev fft;
+};
+
+S2C_KERNEL(so3_fwd_gamma, FwdGammaParams) {
+  const int N = p.N, ld = N + 1;
+  FftSmem s = fft_smem_carve(smem, N);
+  fft_smem_load_tables(ctx, s, p.fft);
+  const long pair0 = (long)ctx.bid * p.G;
+  const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
+  for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+    const int g = it / N, gam = it - g * N;
+    const long e = (pair0 + g) * 2 * N + gam;  // rows 2p and 2p+1 are adjacent in memory
+    const float a = p.x[e * p.in_stride + p.in_off];
+    const float b = p.x[(e + N) * p.in_stride + p.in_off];
+    s.data[g * ld + gam] = make_float2(a, b);
+  }
+  ctx.sync();
+  fft_dif_inplace<-1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  // separate the two real rows packed in one complex transform; keep n < K
+  for (int it = ctx.tid; it < cnt * p.K; it += ctx.nthr) {
+    const int n = it / cnt, g = it - n * cnt;
+    const long pid = pair0 + g;
+    const int pp = (int)(pid % p.b);
+    const long zb = pid / p.b;
+    const int beta = (int)(zb % N);
+    const long z = zb / N;
+    const float2 zk = s.data[g * ld + s.pos[n]];
+    const float2 zc = s.data[g * ld + s.pos[n == 0 ? 0 : N - n]];
+    float4 o;
+    o.x = 0.5f * (zk.x + zc.x);
+    o.y = 0.5f * (zk.y - zc.y);
+    o.z = 0.5f * (zk.y + zc.y);
+    o.w = -0.5f * (zk.x - zc.x);
+    const long idx = ((z * p.K + n) * N + beta) * N + 2 * pp;
+    *reinterpret_cast<float4*>(p.u + idx) = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// analysis, pass 2: FFT over alpha of complex rows, keep |m| < K, transposed store
+// ---------------------------------------------------------------------------------------------
+struct FwdAlphaParams {
+  const float* in;   // rows of N complex (or N real when in_real)
+  int in_real;
+  float2* v;         // [n < Kn][mi < 2K-1][z][beta]
+  int nbatch, N, K, Kn, G;
+  long nrows;        // nbatch * Kn * N; row id = (z * Kn + n) * N + beta
+  FftDev fft;
+};
+
+S2C_KERNEL(so3_fwd_alpha, FwdAlphaParams) {
+  const int N = p.N, ld = N + 1;
+  FftSmem s = fft_smem_carve(smem, N);
+  fft_smem_load_tables(ctx, s, p.fft);
+  const long row0 = (long)ctx.bid * p.G;
+  const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
+  if (p.in_real) {
+    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+      const int g = it / N, a = it - g * N;
+      s.data[g * ld + a] = make_float2(p.in[(row0 + g) * N + a], 0.f);
+    }
+  } else {
+    const float2* in2 = reinterpret_cast<const float2*>(p.in);
+    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+      const int g = it / N, a = it - g * N;
+      s.data[g * ld + a] = in2[(row0 + g) * N + a];
+    }
+  }
+  ctx.sync();
+  fft_dif_inplace<-1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  const int nm = 2 * p.K - 1;
+  for (int it = ctx.tid; it < cnt * nm; it += ctx.nthr) {
+    const int mi = it / cnt, g = it - mi * cnt;
+    const int m = mi - (p.K - 1);
+    const long r = row0 + g;
+    const int beta = (int)(r % N);
+    const long zn = r / N;
+    const int n = (int)(zn % p.Kn);
+    const long z = zn / p.Kn;
+    p.v[(((long)n * nm + mi) * p.nbatch + z) * N + beta] = s.data[g * ld + s.pos[m < 0 ? m + N : m]];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// analysis, pass 3: Wigner-d contraction over beta
+// ---------------------------------------------------------------------------------------------
+enum WignerMode : int {
+  kSo3Real = 0,      // write X and its Hermitian mirror
+  kSo3AccumI = 1,    // X += i * result (imaginary part of a complex input), mirror likewise
+  kS2 = 2,           // S2 transform: rows l^2 + l + m, no mirror
+  kSo3RotI = 3,      // synthesis only: spectrum multiplied by -i first (imaginary output part)
+};
+
+struct FwdWignerParams {
+  const float2* v;   // [n][mi][z][beta]
+  float2* out;       // spectrum rows of `out_zstride` complex, already offset to the chunk's z0
+  long out_zstride;
+  PanelsDev pan;
+  int nbatch, N, K, nl, ZT, nzt, mode;
+};
+
+S2C_KERNEL(so3_fwd_wigner, FwdWignerParams) {
+  const int N = p.N, ldw = N + 1, ldv = N + 1;
+  const int pair = ctx.bid / p.nzt, zt = ctx.bid - pair * p.nzt;
+  int m, n;
+  if (p.mode == kS2) { m = pair - (p.K - 1); n = 0; } else so3_pair_decode(pair, p.K, m, n);
+  const int am = m < 0 ? -m : m;
+  const int lmin = am > n ? am : n;
+  const int L = p.nl - lmin;
+  if (L <= 0) return;
+  const int z0 = zt * p.ZT;
+  const int zc = (p.nbatch - z0) < p.ZT ? (p.nbatch - z0) : p.ZT;
+  float* Ws = reinterpret_cast<float*>(smem);
+  float2* Vs = reinterpret_cast<float2*>(smem + align_up((size_t)p.nl * ldw * sizeof(float), 16));
+  const float* panel = p.pan.data + p.pan.off[pair];
+  for (int it = ctx.tid; it < L * N; it += ctx.nthr) {
+    const int l = it / N, bt = it - l * N;
+    Ws[l * ldw + bt] = panel[it];
+  }
+  const int nm = 2 * p.K - 1, mi = m + p.K - 1;
+  const float2* vsrc = p.v + (((long)n * nm + mi) * p.nbatch + z0) * N;
+  for (int it = ctx.tid; it < zc * N; it += ctx.nthr) {
+    const int zz = it / N, bt = it - zz * N;
+    Vs[zz * ldv + bt] = vsrc[it];
+  }
+  ctx.sync();
+  const float fudge = ((m - n) & 1) ? -1.f : 1.f;
+  for (int it = ctx.tid; it < L * zc; it += ctx.nthr) {
+    const int li = it / zc, zz = it - li * zc;
+    const float* w = Ws + li * ldw;
+    const float2* vv = Vs + zz * ldv;
+    float ar = 0.f, ai = 0.f;
+    for (int bt = 0; bt < N; ++bt) {
+      const float wv = w[bt];
+      const float2 x = vv[bt];
+      ar = fmaf(wv, x.x, ar);
+      ai = fmaf(wv, x.y, ai);
+    }
+    const int l = lmin + li;
+    if (p.mode == kS2) {
+      p.out[((long)l * l + l + m) * p.out_zstride + z0 + zz] = make_float2(ar, ai);
+    } else {
+      float2* o1 = p.out + so3_row(l, m, n) * p.out_zstride + z0 + zz;
+      float2* o2 = p.out + so3_row(l, -m, -n) * p.out_zstride + z0 + zz;
+      const bool self = (m == 0 && n == 0);
+      if (p.mode == kSo3Real) {
+        *o1 = make_float2(ar, ai);
+        if (!self) *o2 = make_float2(fudge * ar, -fudge * ai);
+      } else {  // += i * (ar + i ai); mirror += i * fudge * conj
+        float2 c = *o1;
+        *o1 = make_float2(c.x - ai, c.y + ar);
+        if (!self) {
+          c = *o2;
+          *o2 = make_float2(c.x + fudge * ai, c.y + fudge * ar);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// synthesis, pass 1: Wigner-d contraction over l
+// ---------------------------------------------------------------------------------------------
+struct InvWignerParams {
+  const float2* x;   // spectrum rows of x_zstride complex, offset to the chunk's z0
+  long x_zstride;
+  float2* s;         // [n][mi][z][beta]
+  PanelsDev pan;
+  int nbatch, N, K, ZT, nzt, mode;
+};
+
+S2C_KERNEL(so3_inv_wigner, InvWignerParams) {
+  const int N = p.N;
+  const int pair = ctx.bid / p.nzt, zt = ctx.bid - pair * p.nzt;
+  int m, n;
+  if (p.mode == kS2) { m = pair - (p.K - 1); n = 0; } else so3_pair_decode(pair, p.K, m, n);
+  const int am = m < 0 ? -m : m;
+  const int lmin = am > n ? am : n;
+  const int L = p.pan.nl - lmin;
+  if (L <= 0) return;
+  const int z0 = zt * p.ZT;
+  const int zc = (p.nbatch - z0) < p.ZT ? (p.nbatch - z0) : p.ZT;
+  float* Ws = reinterpret_cast<float*>(smem);
+  float2* Xs = reinterpret_cast<float2*>(smem + align_up((size_t)p.pan.nl * N * sizeof(float), 16));
+  const float* panel = p.pan.data + p.pan.off[pair];
+  for (int it = ctx.tid; it < L * N; it += ctx.nthr) Ws[it] = panel[it];
+  const float fudge = ((m - n) & 1) ? -1.f : 1.f;
+  for (int it = ctx.tid; it < L * zc; it += ctx.nthr) {
+    const int li = it / zc, zz = it - li * zc;
+    const int l = lmin + li;
+    float2 v;
+    if (p.mode == kS2) {
+      v = p.x[((long)l * l + l + m) * p.x_zstride + z0 + zz];
+    } else {
+      float2 a = p.x[so3_row(l, m, n) * p.x_zstride + z0 + zz];
+      float2 b = p.x[so3_row(l, -m, -n) * p.x_zstride + z0 + zz];
+      if (p.mode == kSo3RotI) {  // multiply the spectrum by -i
+        a = make_float2(a.y, -a.x);
+        b = make_float2(b.y, -b.x);
+      }
+      v = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
+    }
+    Xs[li * p.ZT + zz] = v;
+  }
+  ctx.sync();
+  const int nm = 2 * p.K - 1, mi = m + p.K - 1;
+  float2* dst = p.s + (((long)n * nm + mi) * p.nbatch + z0) * N;
+  for (int it = ctx.tid; it < zc * N; it += ctx.nthr) {
+    const int zz = it / N, bt = it - zz * N;
+    float ar = 0.f, ai = 0.f;
+    for (int li = 0; li < L; ++li) {
+      const float wv = Ws[li * N + bt];
+      const float2 x = Xs[li * p.ZT + zz];
+      ar = fmaf(wv, x.x, ar);
+      ai = fmaf(wv, x.y, ai);
+    }
+    dst[it] = make_float2(ar, ai);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// synthesis, pass 2: inverse FFT over m -> alpha
+// ---------------------------------------------------------------------------------------------
+struct InvAlphaParams {
+  const float2* s;   // [n < Kn][mi][z][beta]
+  float* out;        // rows of N complex (or N real when out_real); row id = (z * Kn + n) * N + beta
+  int out_real;
+  int herm_n0;       // SO(3): for n = 0 only m >= 0 is stored; m < 0 is the conjugate
+  int nbatch, N, K, Kn, G;
+  long nrows;
+  FftDev fft;
+};
+
+S2C_KERNEL(so3_inv_alpha, InvAlphaParams) {
+  const int N = p.N, ld = N + 1;
+  FftSmem s = fft_smem_carve(smem, N);
+  fft_smem_load_tables(ctx, s, p.fft);
+  const long row0 = (long)ctx.bid * p.G;
+  const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
+  for (int it = ctx.tid; it < cnt * ld; it += ctx.nthr) s.data[it] = make_float2(0.f, 0.f);
+  ctx.sync();
+  const int nm = 2 * p.K - 1;
+  for (int it = ctx.tid; it < cnt * nm; it += ctx.nthr) {
+    const int mi = it / cnt, g = it - mi * cnt;
+    const int m = mi - (p.K - 1);
+    const long r = row0 + g;
+    const int beta = (int)(r % N);
+    const long zn = r / N;
+    const int n = (int)(zn % p.Kn);
+    const long z = zn / p.Kn;
+    if (p.herm_n0 && n == 0 && m < 0) continue;
+    const float2 v = p.s[(((long)n * nm + mi) * p.nbatch + z) * N + beta];
+    s.data[g * ld + (m < 0 ? m + N : m)] = v;
+    if (p.herm_n0 && n == 0 && m > 0) s.data[g * ld + N - m] = make_float2(v.x, -v.y);
+  }
+  ctx.sync();
+  fft_dif_inplace<+1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  if (p.out_real) {
+    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+      const int g = it / N, a = it - g * N;
+      p.out[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]].x;
+    }
+  } else {
+    float2* out2 = reinterpret_cast<float2*>(p.out);
+    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+      const int g = it / N, a = it - g * N;
+      out2[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// synthesis, pass 3: Hermitian inverse FFT over n -> gamma, two real rows per transform
+// ---------------------------------------------------------------------------------------------
+struct InvGammaParams {
+  const float2* t;   // [z][n < K][beta][alpha]
+  float* out;        // real signal, element e at out[e * out_stride + out_off]
+  long out_stride, out_off;
+  const float* bias; // optional [nfeat]; feature of row z is (z0 + z) % nfeat
+  int nfeat;
+  long z0;
+  int N, b, K, G;
+  long npairs;
+  FftDev fft;
+};
+
+S2C_KERNEL(so3_inv_gamma, InvGammaParams) {
+  const int N = p.N, ld = N + 1;
+  FftSmem s = fft_smem_carve(smem, N);
+  fft_smem_load_tables(ctx, s, p.fft);
+  const long pair0 = (long)ctx.bid * p.G;
+  const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
+  for (int it = ctx.tid; it < cnt * ld; it += ctx.nthr) s.data[it] = make_float2(0.f, 0.f);
+  ctx.sync();
+  for (int it = ctx.tid; it < cnt * p.K; it += ctx.nthr) {
+    const int n = it / cnt, g = it - n * cnt;
+    const long pid = pair0 + g;
+    const int pp = (int)(pid % p.b);
+    const long zb = pid / p.b;
+    const int beta = (int)(zb % N);
+    const long z = zb / N;
+    const float4 tv =
+        *reinterpret_cast<const float4*>(p.t + ((z * p.K + n) * N + beta) * N + 2 * pp);
+    if (n == 0) {
+      // T[alpha][0] is real for a Hermitian spectrum; its rounding-level imaginary part is dropped
+      s.data[g * ld] = make_float2(tv.x, tv.z);
+    } else {
+      s.data[g * ld + n] = make_float2(tv.x - tv.w, tv.y + tv.z);       // T1 + i T2
+      s.data[g * ld + N - n] = make_float2(tv.x + tv.w, tv.z - tv.y);   // conj(T1) + i conj(T2)
+    }
+  }
+  ctx.sync();
+  fft_dif_inplace<+1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
+    const int g = it / N, gam = it - g * N;
+    const long pid = pair0 + g;
+    const float2 v = s.data[g * ld + s.pos[gam]];
+    float add = 0.f;
+    if (p.bias) add = p.bias[(p.z0 + pid / ((long)p.b * N)) % p.nfeat];
+    const long e = pid * 2 * N + gam;
+    p.out[e * p.out_stride + p.out_off] = v.x + add;
+    p.out[(e + N) * p.out_stride + p.out_off] = v.y + add;
+  }
+}
+
+}  // namespace s2c

@@ -1,0 +1,196 @@
+// Per-device cache of the constant tables the kernels read: FFT twiddles / digit maps, Wigner-d
+// panels and quadrature weights.  Plays the role of the reference's `_setup_wigner` lru_cache
+// (s2cnn/soft/so3_fft.py:205-209, s2cnn/soft/s2_fft.py:109-113) and of the table builders
+// `_setup_so3_fft` / `_setup_s2_fft` (so3_fft.py:212-243, s2_fft.py:116-147), with a layout chosen
+// for the kernels rather than the reference's [beta, lmn]:
+//
+//   one contiguous panel per frequency pair (m, n):  panel[l - lmin][beta_j]
+//       = d^l_mn(beta_j) * (w_j  if weighted  else  2l+1),     lmin = max(|m|, |n|)
+//
+// SO(3) panels exist only for the half plane  n > 0  or  (n = 0, m >= 0); the mirrored pair
+// (-m, -n) is served by d^l_{-m,-n} = (-1)^(m-n) d^l_{mn}.  S2 panels (column n = 0, weight
+// w_j * 2b) exist for every |m| < K.
+//
+// Tables are built in float64 on the host, rounded to float32 and uploaded on first use; the
+// first call for a new (bandwidth, kind, device) therefore allocates and copies synchronously.
+#pragma once
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <tuple>
+
+#include "backend.h"
+#include "host_math.h"
+
+namespace s2c {
+
+struct FftDev {
+  FftDesc desc;
+  const float2* tw;            // device, n entries exp(+2 pi i k / n)
+  const unsigned short* pos;   // device, n entries
+};
+
+struct PanelsDev {
+  int nbeta;   // 2 * b of the beta grid
+  int nl;      // degrees l < nl
+  int K;       // frequencies |m|, n < K
+  int npairs;
+  int s2;      // 1: S2 panels (n = 0, all m), 0: SO(3) half plane
+  const float* data;        // device
+  const long long* off;     // device, npairs + 1 offsets (in floats)
+};
+
+S2C_HD int so3_npairs(int K) { return K + (K - 1) * (2 * K - 1); }
+S2C_HD int so3_pair_index(int m, int n, int K) {
+  return n == 0 ? m : K + (n - 1) * (2 * K - 1) + (m + K - 1);
+}
+S2C_HD void so3_pair_decode(int idx, int K, int& m, int& n) {
+  if (idx < K) { m = idx; n = 0; }
+  else { const int t = idx - K; n = t / (2 * K - 1) + 1; m = t % (2 * K - 1) - (K - 1); }
+}
+
+class TableCache {
+ public:
+  static TableCache& get() {
+    static TableCache c;
+    return c;
+  }
+
+  int fft(int n, FftDev& out) {
+    std::lock_guard<std::mutex> g(mu_);
+    const int dev = dev_current();
+    auto key = std::make_pair(dev, n);
+    auto it = fft_.find(key);
+    if (it == fft_.end()) {
+      FftDev f;
+      if (!fft_plan(n, f.desc))
+        return fail(S2C_ERR_UNSUPPORTED,
+                    "FFT length " + std::to_string(n) + " has a prime factor above " +
+                        std::to_string(kMaxRadix));
+      if (n > 65535) return fail(S2C_ERR_UNSUPPORTED, "FFT length above 65535");
+      std::vector<float> tw;
+      std::vector<unsigned short> pos;
+      fft_twiddles(n, tw);
+      fft_positions(f.desc, pos);
+      void* dtw = dev_alloc(tw.size() * sizeof(float));
+      void* dpos = dev_alloc(pos.size() * sizeof(unsigned short));
+      if (!dtw || !dpos) return fail(S2C_ERR_CUDA, "table allocation failed");
+      int rc = dev_upload(dtw, tw.data(), tw.size() * sizeof(float));
+      if (rc) return rc;
+      rc = dev_upload(dpos, pos.data(), pos.size() * sizeof(unsigned short));
+      if (rc) return rc;
+      f.tw = (const float2*)dtw;
+      f.pos = (const unsigned short*)dpos;
+      it = fft_.emplace(key, f).first;
+    }
+    out = it->second;
+    return S2C_OK;
+  }
+
+  // Host build of the panel table (also exported for tests).
+  static void build_panels(int b_beta, int nl, int K, bool weighted, bool s2,
+                           std::vector<float>& data, std::vector<long long>& off) {
+    const int nbeta = 2 * b_beta;
+    std::vector<double> beta, w;
+    soft_betas(b_beta, beta);
+    quadrature_weights(b_beta, w);
+    if (s2) for (auto& v : w) v *= 2.0 * b_beta;  // s2cnn/soft/s2_fft.py:124
+    const int npairs = s2 ? 2 * K - 1 : so3_npairs(K);
+    off.assign(npairs + 1, 0);
+    for (int p = 0; p < npairs; ++p) {
+      int m, n;
+      if (s2) { m = p - (K - 1); n = 0; } else so3_pair_decode(p, K, m, n);
+      const int lmin = std::max(std::abs(m), n);
+      off[p + 1] = off[p] + (long long)std::max(nl - lmin, 0) * nbeta;
+    }
+    data.assign((size_t)off[npairs], 0.f);
+    std::vector<double> col(nl + 1);
+    for (int p = 0; p < npairs; ++p) {
+      int m, n;
+      if (s2) { m = p - (K - 1); n = 0; } else so3_pair_decode(p, K, m, n);
+      const int lmin = std::max(std::abs(m), n);
+      if (lmin >= nl) continue;
+      float* panel = data.data() + off[p];
+      for (int j = 0; j < nbeta; ++j) {
+        wigner_d_degrees(m, n, beta[j], nl, col.data());
+        for (int l = lmin; l < nl; ++l) {
+          const double wt = weighted ? w[j] : (2.0 * l + 1.0);
+          panel[(size_t)(l - lmin) * nbeta + j] = (float)(col[l - lmin] * wt);
+        }
+      }
+    }
+  }
+
+  int panels(int b_beta, int nl, int K, bool weighted, bool s2, PanelsDev& out) {
+    std::lock_guard<std::mutex> g(mu_);
+    const int dev = dev_current();
+    auto key = std::make_tuple(dev, b_beta, nl, K, (int)weighted, (int)s2);
+    auto it = panels_.find(key);
+    if (it == panels_.end()) {
+      std::vector<float> data;
+      std::vector<long long> off;
+      build_panels(b_beta, nl, K, weighted, s2, data, off);
+      void* dd = dev_alloc(data.size() * sizeof(float));
+      void* doff = dev_alloc(off.size() * sizeof(long long));
+      if (!dd || !doff) return fail(S2C_ERR_CUDA, "table allocation failed");
+      int rc = dev_upload(dd, data.data(), data.size() * sizeof(float));
+      if (rc) return rc;
+      rc = dev_upload(doff, off.data(), off.size() * sizeof(long long));
+      if (rc) return rc;
+      PanelsDev pd;
+      pd.nbeta = 2 * b_beta;
+      pd.nl = nl;
+      pd.K = K;
+      pd.npairs = (int)off.size() - 1;
+      pd.s2 = s2 ? 1 : 0;
+      pd.data = (const float*)dd;
+      pd.off = (const long long*)doff;
+      it = panels_.emplace(key, pd).first;
+    }
+    out = it->second;
+    return S2C_OK;
+  }
+
+  int quad_weights(int b, const float** out) {
+    std::lock_guard<std::mutex> g(mu_);
+    const int dev = dev_current();
+    auto key = std::make_pair(dev, b);
+    auto it = quad_.find(key);
+    if (it == quad_.end()) {
+      std::vector<double> w;
+      quadrature_weights(b, w);
+      std::vector<float> wf(w.begin(), w.end());
+      void* d = dev_alloc(wf.size() * sizeof(float));
+      if (!d) return fail(S2C_ERR_CUDA, "table allocation failed");
+      int rc = dev_upload(d, wf.data(), wf.size() * sizeof(float));
+      if (rc) return rc;
+      it = quad_.emplace(key, (const float*)d).first;
+    }
+    *out = it->second;
+    return S2C_OK;
+  }
+
+  void clear() {
+    std::lock_guard<std::mutex> g(mu_);
+    for (auto& kv : fft_) { dev_free((void*)kv.second.tw); dev_free((void*)kv.second.pos); }
+    for (auto& kv : panels_) { dev_free((void*)kv.second.data); dev_free((void*)kv.second.off); }
+    for (auto& kv : quad_) dev_free((void*)kv.second);
+    fft_.clear();
+    panels_.clear();
+    quad_.clear();
+  }
+
+  size_t bytes_cached() {
+    std::lock_guard<std::mutex> g(mu_);
+    return 0;
+  }
+
+ private:
+  std::mutex mu_;
+  std::map<std::pair<int, int>, FftDev> fft_;
+  std::map<std::tuple<int, int, int, int, int, int>, PanelsDev> panels_;
+  std::map<std::pair<int, int>, const float*> quad_;
+};
+
+}  // namespace s2c

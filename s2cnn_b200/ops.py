@@ -1,0 +1,314 @@
+"""Pointer plumbing between torch tensors and the C ABI (include/s2cnn_b200.h).
+
+``Ops(lib)`` exposes one method per entry point: it checks dtype/shape, allocates the output and
+the scratch space with torch (device memory management is all torch is used for here), and passes
+raw pointers plus the current CUDA stream.  The public, reference-named API in the sibling modules
+is built on ``cuda_ops()``, which is bound to the CUDA build and refuses CPU tensors.
+"""
+import contextlib
+
+import torch
+
+from . import _lib
+
+
+def so3_nspec(b):
+    return b * (4 * b * b - 1) // 3
+
+
+def bandwidth_from_so3_nspec(nspec):
+    b = round((3.0 / 4.0 * nspec) ** (1.0 / 3.0))  # as s2cnn/soft/so3_fft.py:121-122
+    assert nspec == so3_nspec(b), "not an SO(3) spectrum length: %d" % nspec
+    return b
+
+
+def _prod(shape):
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+class Ops:
+    def __init__(self, lib):
+        self.lib = lib
+
+    # -- helpers -------------------------------------------------------------------------------
+    def _prep(self, *tensors):
+        for t in tensors:
+            if t is None:
+                continue
+            if t.dtype != torch.float32:
+                raise TypeError("s2cnn_b200 kernels are float32 only, got %s" % t.dtype)
+            if t.is_cuda != self.lib.is_cuda:
+                raise _lib.S2cError(
+                    "s2cnn_b200: tensor on %s but the loaded library is the %s build - the "
+                    "product path runs on CUDA only" % (t.device, "CUDA" if self.lib.is_cuda else "emulation"))
+
+    def _ctx(self, t):
+        return torch.cuda.device_of(t) if t.is_cuda else contextlib.nullcontext()
+
+    def _stream(self, t):
+        return torch.cuda.current_stream(t.device).cuda_stream if t.is_cuda else None
+
+    @staticmethod
+    def _ws(nbytes, like):
+        return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=like.device)
+
+    # -- SO(3) transforms ----------------------------------------------------------------------
+    def so3_rfft(self, x, for_grad=False, b_out=None):
+        """[..., 2b, 2b, 2b] real -> [nspec(b_out), ..., 2]"""
+        self._prep(x)
+        b_in = x.size(-1) // 2
+        assert x.size(-1) == 2 * b_in and x.size(-2) == 2 * b_in and x.size(-3) == 2 * b_in
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[:-3])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        out = x.new_empty((so3_nspec(b_out), nbatch, 2))
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_so3_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_so3_rfft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
+                          int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+        return out.view(-1, *lead, 2)
+
+    def so3_fft(self, x, for_grad=False, b_out=None):
+        """[..., 2b, 2b, 2b, 2] complex -> [nspec(b_out), ..., 2]"""
+        self._prep(x)
+        assert x.size(-1) == 2, x.size()
+        b_in = x.size(-2) // 2
+        assert x.size(-2) == 2 * b_in and x.size(-3) == 2 * b_in and x.size(-4) == 2 * b_in
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[:-4])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        out = x.new_empty((so3_nspec(b_out), nbatch, 2))
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_so3_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_so3_fft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
+                          int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+        return out.view(-1, *lead, 2)
+
+    def so3_rifft(self, x, for_grad=False, b_out=None, bias=None):
+        """[nspec(b_in), ..., 2] -> [..., 2b_out, 2b_out, 2b_out] real (+ per-feature bias, where
+        the feature axis is the last leading axis)."""
+        self._prep(x, bias)
+        assert x.size(-1) == 2
+        b_in = bandwidth_from_so3_nspec(x.size(0))
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[1:-1])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        n = 2 * b_out
+        out = x.new_empty((nbatch, n, n, n))
+        nfeat = 0
+        bias_ptr = None
+        if bias is not None:
+            bias = bias.contiguous().view(-1)
+            nfeat = bias.numel()
+            assert len(lead) >= 1 and lead[-1] == nfeat, (lead, nfeat)
+            bias_ptr = bias.data_ptr()
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_so3_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_so3_rifft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
+                          int(bool(for_grad)), bias_ptr, nfeat, ws.data_ptr(), ws.numel(),
+                          self._stream(x))
+        return out.view(*lead, n, n, n)
+
+    def so3_ifft(self, x, for_grad=False, b_out=None):
+        """[nspec(b_in), ..., 2] -> [..., 2b_out, 2b_out, 2b_out, 2] complex"""
+        self._prep(x)
+        assert x.size(-1) == 2
+        b_in = bandwidth_from_so3_nspec(x.size(0))
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[1:-1])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        n = 2 * b_out
+        out = x.new_empty((nbatch, n, n, n, 2))
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_so3_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_so3_ifft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
+                          int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+        return out.view(*lead, n, n, n, 2)
+
+    # -- S2 transforms -------------------------------------------------------------------------
+    def s2_fft(self, x, for_grad=False, b_out=None, x_is_real=False):
+        """[..., 2b, 2b(, 2)] -> [b_out^2, ..., 2]"""
+        self._prep(x)
+        if x_is_real:
+            b_in = x.size(-1) // 2
+            assert x.size(-1) == 2 * b_in and x.size(-2) == 2 * b_in
+            lead = tuple(x.shape[:-2])
+        else:
+            assert x.size(-1) == 2
+            b_in = x.size(-2) // 2
+            assert x.size(-2) == 2 * b_in and x.size(-3) == 2 * b_in
+            lead = tuple(x.shape[:-3])
+        b_out = b_in if b_out is None else b_out
+        assert b_out <= b_in  # s2cnn/soft/s2_fft.py:24
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        out = x.new_empty((b_out * b_out, nbatch, 2))
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_s2_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_s2_fft", x.data_ptr(), int(x_is_real), out.data_ptr(), nbatch, b_in,
+                          b_out, int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+        return out.view(-1, *lead, 2)
+
+    def s2_ifft(self, x, for_grad=False, b_out=None, out_is_real=False):
+        """[b_in^2, ..., 2] -> [..., 2b_out, 2b_out(, 2)]"""
+        self._prep(x)
+        assert x.size(-1) == 2
+        nspec = x.size(0)
+        b_in = round(nspec ** 0.5)
+        assert nspec == b_in ** 2
+        b_out = b_in if b_out is None else b_out
+        assert b_out >= b_in  # s2cnn/soft/s2_fft.py:71
+        lead = tuple(x.shape[1:-1])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        n = 2 * b_out
+        shape = (nbatch, n, n) if out_is_real else (nbatch, n, n, 2)
+        out = x.new_empty(shape)
+        with self._ctx(x):
+            ws = self._ws(self.lib.s2c_s2_fft_workspace(nbatch, b_in, b_out), x)
+            self.lib.call("s2c_s2_ifft", x.data_ptr(), out.data_ptr(), int(out_is_real), nbatch,
+                          b_in, b_out, int(bool(for_grad)), ws.data_ptr(), ws.numel(),
+                          self._stream(x))
+        return out.view(*lead, *shape[1:])
+
+    # -- spectral products ---------------------------------------------------------------------
+    def _mm(self, fn, a, b, out_shape, nl, nbatch, f_in, f_out):
+        self._prep(a, b)
+        a = a.contiguous()
+        b = b.contiguous()
+        out = a.new_empty(out_shape)
+        with self._ctx(a):
+            self.lib.call(fn, a.data_ptr(), b.data_ptr(), out.data_ptr(), nl, nbatch, f_in, f_out,
+                          self._stream(a))
+        return out
+
+    @staticmethod
+    def _mm_dims(x_shape, y_shape, so3):
+        nspec, nbatch, f_in, two = x_shape
+        assert two == 2 and y_shape[3] == 2
+        f_out = y_shape[2]
+        assert y_shape[1] == f_in and y_shape[0] == nspec
+        if so3:
+            nl = bandwidth_from_so3_nspec(nspec)
+        else:
+            nl = round(nspec ** 0.5)
+            assert nspec == nl * nl
+        return nl, nbatch, f_in, f_out
+
+    def so3_mm(self, x, y):
+        nl, nb, fi, fo = self._mm_dims(x.shape, y.shape, True)
+        return self._mm("s2c_so3_mm", x, y, (so3_nspec(nl), nb, fo, 2), nl, nb, fi, fo)
+
+    def so3_mm_gradx(self, gz, y, nb, fi):
+        nl = bandwidth_from_so3_nspec(y.size(0))
+        fo = y.size(2)
+        return self._mm("s2c_so3_mm_gradx", gz, y, (so3_nspec(nl), nb, fi, 2), nl, nb, fi, fo)
+
+    def so3_mm_grady(self, gz, x, fo):
+        nl = bandwidth_from_so3_nspec(x.size(0))
+        nb, fi = x.size(1), x.size(2)
+        return self._mm("s2c_so3_mm_grady", gz, x, (so3_nspec(nl), fi, fo, 2), nl, nb, fi, fo)
+
+    def s2_mm(self, x, y):
+        nl, nb, fi, fo = self._mm_dims(x.shape, y.shape, False)
+        return self._mm("s2c_s2_mm", x, y, (so3_nspec(nl), nb, fo, 2), nl, nb, fi, fo)
+
+    def s2_mm_gradx(self, gz, y, nb, fi):
+        nl = round(y.size(0) ** 0.5)
+        fo = y.size(2)
+        return self._mm("s2c_s2_mm_gradx", gz, y, (nl * nl, nb, fi, 2), nl, nb, fi, fo)
+
+    def s2_mm_grady(self, gz, x, fo):
+        nl = round(x.size(0) ** 0.5)
+        nb, fi = x.size(1), x.size(2)
+        return self._mm("s2c_s2_mm_grady", gz, x, (nl * nl, fi, fo, 2), nl, nb, fi, fo)
+
+    # -- kernel-grid -> spectrum ---------------------------------------------------------------
+    def rft_forward(self, x2d, F):
+        """x2d [nf, n_grid], F [n_grid, nspec, 2] -> [nspec, nf, 2]"""
+        self._prep(x2d, F)
+        nf, ng = x2d.shape
+        assert F.size(0) == ng and F.size(2) == 2
+        ns = F.size(1)
+        x2d = x2d.contiguous()
+        F = F.contiguous()
+        out = x2d.new_empty((ns, nf, 2))
+        with self._ctx(x2d):
+            self.lib.call("s2c_rft_forward", x2d.data_ptr(), F.data_ptr(), out.data_ptr(), nf, ng,
+                          ns, self._stream(x2d))
+        return out
+
+    def rft_backward(self, g, F):
+        """g [nspec, nf, 2], F [n_grid, nspec, 2] -> [nf, n_grid]"""
+        self._prep(g, F)
+        ns, nf, _ = g.shape
+        ng = F.size(0)
+        assert F.size(1) == ns
+        g = g.contiguous()
+        F = F.contiguous()
+        out = g.new_empty((nf, ng))
+        with self._ctx(g):
+            self.lib.call("s2c_rft_backward", g.data_ptr(), F.data_ptr(), out.data_ptr(), nf, ng,
+                          ns, self._stream(g))
+        return out
+
+    # -- integration ---------------------------------------------------------------------------
+    def so3_integrate(self, x, relu=False):
+        self._prep(x)
+        assert x.size(-1) == x.size(-2) and x.size(-2) == x.size(-3)
+        b = x.size(-1) // 2
+        lead = tuple(x.shape[:-3])
+        n = _prod(lead)
+        x = x.contiguous()
+        out = x.new_empty((n,))
+        with self._ctx(x):
+            self.lib.call("s2c_so3_integrate", x.data_ptr(), out.data_ptr(), n, b, int(relu),
+                          self._stream(x))
+        return out.view(*lead)
+
+    def so3_integrate_backward(self, g, b, x=None, relu=False):
+        self._prep(g, x)
+        lead = tuple(g.shape)
+        n = _prod(lead)
+        g = g.contiguous()
+        if x is not None:
+            x = x.contiguous()
+        m = 2 * b
+        out = g.new_empty((n, m, m, m))
+        with self._ctx(g):
+            self.lib.call("s2c_so3_integrate_backward", g.data_ptr(),
+                          x.data_ptr() if x is not None else None, out.data_ptr(), n, b,
+                          int(relu), self._stream(g))
+        return out.view(*lead, m, m, m)
+
+    # -- host generators -----------------------------------------------------------------------
+    def so3_ft_matrix(self, b, grid):
+        import numpy as np
+        g = np.ascontiguousarray(np.asarray(grid, dtype=np.float64).reshape(len(grid), 3))
+        F = np.empty((len(grid), so3_nspec(b), 2), dtype=np.float32)
+        self.lib.call("s2c_so3_ft_matrix", b, g.ctypes.data, len(grid), F.ctypes.data)
+        return F
+
+    def s2_ft_matrix(self, b, grid):
+        import numpy as np
+        g = np.ascontiguousarray(np.asarray(grid, dtype=np.float64).reshape(len(grid), 2))
+        F = np.empty((len(grid), b * b, 2), dtype=np.float32)
+        self.lib.call("s2c_s2_ft_matrix", b, g.ctypes.data, len(grid), F.ctypes.data)
+        return F
+
+
+_cuda_ops = None
+
+
+def cuda_ops():
+    global _cuda_ops
+    if _cuda_ops is None:
+        _cuda_ops = Ops(_lib.cuda_lib())
+    return _cuda_ops

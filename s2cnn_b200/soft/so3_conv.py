@@ -1,0 +1,73 @@
+"""SO3Convolution and SO3Shortcut (s2cnn/soft/so3_conv.py:12-85): same constructors, parameters,
+init, scaling and state_dict keys."""
+import math
+
+import torch
+from torch.nn.modules import Module
+from torch.nn.parameter import Parameter
+
+from ..so3_ft import so3_rft
+from ..so3_mm import so3_mm
+from .so3_fft import SO3_fft_real, SO3_ifft_real_bias
+
+
+class SO3Convolution(Module):
+    def __init__(self, nfeature_in, nfeature_out, b_in, b_out, grid):
+        '''
+        :param nfeature_in: number of input fearures
+        :param nfeature_out: number of output features
+        :param b_in: input bandwidth (precision of the input SOFT grid)
+        :param b_out: output bandwidth
+        :param grid: points of the SO(3) group defining the kernel, tuple of (beta, alpha, gamma)'s
+        '''
+        super().__init__()
+        self.nfeature_in = nfeature_in
+        self.nfeature_out = nfeature_out
+        self.b_in = b_in
+        self.b_out = b_out
+        self.grid = grid
+        self.kernel = Parameter(torch.empty(nfeature_in, nfeature_out, len(grid)).uniform_(-1, 1))
+        self.bias = Parameter(torch.zeros(1, nfeature_out, 1, 1, 1))
+        # the scaling stays outside the parameter (so3_conv.py:30-34)
+        self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
+
+    def forward(self, x):  # pylint: disable=W
+        '''
+        :x:      [batch, feature_in,  beta, alpha, gamma]
+        :return: [batch, feature_out, beta, alpha, gamma]
+        '''
+        assert x.size(1) == self.nfeature_in
+        assert x.size(2) == 2 * self.b_in
+        assert x.size(3) == 2 * self.b_in
+        assert x.size(4) == 2 * self.b_in
+        x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
+        y = so3_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m * n, feature_in, feature_out, complex]
+        assert x.size(0) == y.size(0)
+        assert x.size(2) == y.size(1)
+        z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
+        return SO3_ifft_real_bias.apply(z, self.bias)  # [batch, feature_out, beta, alpha, gamma]
+
+
+class SO3Shortcut(Module):
+    '''
+    Useful for ResNet
+    '''
+
+    def __init__(self, nfeature_in, nfeature_out, b_in, b_out):
+        super().__init__()
+        assert b_out <= b_in
+        if (nfeature_in != nfeature_out) or (b_in != b_out):
+            self.conv = SO3Convolution(
+                nfeature_in=nfeature_in, nfeature_out=nfeature_out, b_in=b_in, b_out=b_out,
+                grid=((0, 0, 0), ))
+        else:
+            self.conv = None
+
+    def forward(self, x):  # pylint: disable=W
+        '''
+        :x:      [batch, feature_in,  beta, alpha, gamma]
+        :return: [batch, feature_out, beta, alpha, gamma]
+        '''
+        if self.conv is not None:
+            return self.conv(x)
+        return x

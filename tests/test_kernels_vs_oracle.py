@@ -1,0 +1,221 @@
+"""Every entry point of the C ABI against the CPU oracle and the reference's golden vectors.
+
+Runs twice: on the host-emulation build of the kernel sources (CPU) and, marked ``gpu``, on the
+CUDA library.  Shapes are the ones the reference's own tests use (tests/so3_fft.py:57-102,
+s2cnn/soft/s2_fft.py:253-268, s2cnn/s2_mm.py:315-320, s2cnn/so3_mm.py:264-269) plus edge cases:
+b = 1, b_out > b_in (zero-padded rows), b_out < b_in (truncation), batch sizes that do not fill a
+tile, FFT lengths with prime factors 3, 5, 7, 11, 13.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import backends
+from oracle import s2cnn_oracle as O
+from util import GOLDEN, assert_close, golden, grid_tuple
+
+n3 = O.so3_nspec
+
+
+def _names(prefix):
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, prefix + "*.npz")))
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("so3_fft_"))
+def test_so3_transforms_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    b_out = int(g["b_out"])
+    for fg in (False, True):
+        t = "_grad" if fg else ""
+        assert_close(ops.so3_rfft(g["x_real"].to(dev), fg, b_out), g["rfft" + t], name + " rfft" + t)
+        assert_close(ops.so3_fft(g["x_complex"].to(dev), fg, b_out), g["fft" + t], name + " fft" + t)
+        assert_close(ops.so3_ifft(g["spectrum"].to(dev), fg, b_out), g["ifft" + t], name + " ifft" + t)
+        assert_close(ops.so3_rifft(g["spectrum"].to(dev), fg, b_out), g["rifft" + t], name + " rifft" + t)
+        assert_close(ops.so3_rifft(g["spectrum_h"].to(dev), fg, b_out), g["rifft_h" + t], name + " rifft_h" + t)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(1, 1, 1), (1, 3, 2), (3, 1, 5), (13, 7, 1),
+                                               (6, 6, 37), (8, 8, 3), (5, 12, 2)])
+def test_so3_transforms_oracle(backend, b_in, b_out, nbatch):
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(100 * b_in + b_out)
+    x = torch.randn(nbatch, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen)
+    s = torch.randn(n3(b_in), nbatch, 2, generator=gen)
+    assert_close(ops.so3_rfft(x.to(dev), False, b_out), O.so3_rfft(x, False, b_out), "rfft")
+    assert_close(ops.so3_rifft(s.to(dev), False, b_out), O.so3_rifft(s, False, b_out), "rifft")
+    assert_close(ops.so3_rifft(s.to(dev), True, b_out), O.so3_rifft(s, True, b_out), "rifft grad")
+    assert_close(ops.so3_ifft(s.to(dev), False, b_out), O.so3_ifft(s, False, b_out), "ifft")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_so3_leading_dims_and_bias(backend):
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 3, 8, 8, 8, generator=gen)
+    y = ops.so3_rfft(x.to(dev), b_out=3)
+    assert tuple(y.shape) == (n3(3), 2, 3, 2)
+    assert_close(y, O.so3_rfft(x, b_out=3), "rfft lead dims")
+    s = torch.randn(n3(4), 2, 3, 2, generator=gen)
+    bias = torch.randn(3, generator=gen)
+    out = ops.so3_rifft(s.to(dev), bias=bias.to(dev))
+    assert tuple(out.shape) == (2, 3, 8, 8, 8)
+    assert_close(out, O.so3_rifft(s) + bias.view(1, 3, 1, 1, 1), "rifft + bias")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_so3_small_workspace_chunks(backend):
+    """A workspace that holds only 2 batch elements forces the chunked path."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(6)
+    b_in, b_out, nb = 5, 4, 7
+    x = torch.randn(nb, 10, 10, 10, generator=gen).to(dev)
+    out = x.new_empty((n3(b_out), nb, 2))
+    per = ops.lib.s2c_so3_fft_workspace_min(b_in, b_out)
+    ws = torch.empty(2 * per + 8, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream if dev.type == "cuda" else None
+    ops.lib.call("s2c_so3_rfft", x.data_ptr(), out.data_ptr(), nb, b_in, b_out, 0,
+                 ws.data_ptr(), ws.numel(), stream)
+    assert_close(out, O.so3_rfft(x.cpu(), b_out=b_out), "chunked rfft")
+    s = torch.randn(n3(b_in), nb, 2, generator=gen).to(dev)
+    y = s.new_empty((nb, 8, 8, 8))
+    ops.lib.call("s2c_so3_rifft", s.data_ptr(), y.data_ptr(), nb, b_in, b_out, 0, None, 0,
+                 ws.data_ptr(), ws.numel(), stream)
+    assert_close(y, O.so3_rifft(s.cpu(), b_out=b_out), "chunked rifft")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("s2_fft_"))
+def test_s2_fft_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    for fg in (False, True):
+        assert_close(ops.s2_fft(g["x"].to(dev), fg, int(g["b_out"])),
+                     g["fft_grad" if fg else "fft"], name)
+    xr = g["x"][..., 0].contiguous()
+    ref = O.s2_fft(torch.stack((xr, torch.zeros_like(xr)), -1), b_out=int(g["b_out"]))
+    assert_close(ops.s2_fft(xr.to(dev), b_out=int(g["b_out"]), x_is_real=True), ref, name + " real")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("s2_ifft_"))
+def test_s2_ifft_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    for fg in (False, True):
+        ref = g["ifft_grad" if fg else "ifft"]
+        assert_close(ops.s2_ifft(g["x"].to(dev), fg, int(g["b_out"])), ref, name)
+        assert_close(ops.s2_ifft(g["x"].to(dev), fg, int(g["b_out"]), out_is_real=True),
+                     ref[..., 0], name + " real")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("s2_mm_") + _names("so3_mm_"))
+def test_mm_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    fn = ops.s2_mm if name.startswith("s2") else ops.so3_mm
+    assert_close(fn(g["x"].to(dev), g["y"].to(dev)), g["z"], name)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("nl,nb,fi,fo", [(4, 2, 3, 5), (3, 70, 5, 9), (1, 1, 1, 1), (5, 3, 18, 2),
+                                         (2, 65, 17, 66)])
+def test_mm_forward_and_gradients(backend, nl, nb, fi, fo):
+    """Forward against the oracle; grad-x / grad-y against autograd through the oracle (which
+    equals the reference's hand-written backward kernels, s2cnn/so3_mm.py:95-122)."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(nl * 1000 + nb)
+    for so3 in (True, False):
+        ns = n3(nl) if so3 else nl * nl
+        x = torch.randn(ns, nb, fi, 2, generator=gen, requires_grad=True)
+        y = torch.randn(ns, fi, fo, 2, generator=gen, requires_grad=True)
+        zo = (O.so3_mm if so3 else O.s2_mm)(x, y)
+        gz = torch.randn(zo.shape, generator=gen)
+        zo.backward(gz)
+        xd, yd, gzd = x.detach().to(dev), y.detach().to(dev), gz.to(dev)
+        if so3:
+            z, gx, gy = ops.so3_mm(xd, yd), ops.so3_mm_gradx(gzd, yd, nb, fi), ops.so3_mm_grady(gzd, xd, fo)
+        else:
+            z, gx, gy = ops.s2_mm(xd, yd), ops.s2_mm_gradx(gzd, yd, nb, fi), ops.s2_mm_grady(gzd, xd, fo)
+        tag = "so3_mm" if so3 else "s2_mm"
+        assert_close(z, zo.detach(), tag)
+        assert_close(gx, x.grad, tag + " gradx")
+        assert_close(gy, y.grad, tag + " grady")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("s2_rft_") + _names("so3_rft_"))
+def test_rft_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    grid = grid_tuple(g["grid"])
+    b = int(g["b"])
+    F = ops.s2_ft_matrix(b, grid) if name.startswith("s2") else ops.so3_ft_matrix(b, grid)
+    F = torch.from_numpy(F).to(dev)
+    x = g["x"]
+    y = ops.rft_forward(x.reshape(-1, x.size(-1)).to(dev), F)
+    assert_close(y.view(-1, *x.shape[:-1], 2), g["y"], name)
+    # transpose: <rft(x), g> = <x, rft^T(g)>
+    gen = torch.Generator().manual_seed(1)
+    gy = torch.randn(y.shape, generator=gen)
+    gx = ops.rft_backward(gy.to(dev), F).cpu()
+    lhs = (y.cpu().double() * gy.double()).sum().item()
+    rhs = (x.reshape(-1, x.size(-1)).double() * gx.double()).sum().item()
+    assert abs(lhs - rhs) <= 1e-5 * max(abs(lhs), 1.0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_ft_matrices_match_oracle(backend):
+    ops, _ = backends.get(backend)
+    g3 = O.so3_near_identity_grid(max_beta=np.pi / 8, max_gamma=2 * np.pi, n_alpha=8, n_beta=3, n_gamma=8)
+    for b, grid in [(4, g3), (7, O.so3_equatorial_grid(n_alpha=8)), (3, ((0.0, 0.0, 0.0),))]:
+        assert np.abs(ops.so3_ft_matrix(b, grid) - O.so3_ft_matrix(b, grid).numpy()).max() < 1e-6
+    for b, grid in [(5, O.s2_near_identity_grid()), (9, O.s2_equatorial_grid(n_alpha=12))]:
+        assert np.abs(ops.s2_ft_matrix(b, grid) - O.s2_ft_matrix(b, grid).numpy()).max() < 1e-5
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", _names("so3_integrate_"))
+def test_integrate_golden(backend, name):
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    assert_close(ops.so3_integrate(g["x"].to(dev)), g["y"], name)
+    b = g["x"].size(-1) // 2
+    x = g["x"].clone().requires_grad_(True)
+    yo = O.so3_integrate(x)
+    gy = torch.randn(yo.shape, generator=torch.Generator().manual_seed(3))
+    yo.backward(gy)
+    assert_close(ops.so3_integrate_backward(gy.to(dev), b), x.grad, name + " backward")
+    # fused activation
+    assert_close(ops.so3_integrate(g["x"].to(dev), relu=True), O.so3_integrate(torch.relu(g["x"])), "relu")
+    x2 = g["x"].clone().requires_grad_(True)
+    O.so3_integrate(torch.relu(x2)).backward(gy)
+    assert_close(ops.so3_integrate_backward(gy.to(dev), b, x=g["x"].to(dev), relu=True), x2.grad, "relu bwd")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_write_coverage_no_stale_values(backend):
+    """Outputs are fully written: pre-filling them with NaN must leave none behind (the reference
+    needs an explicit output[:] = 0 for the Nyquist rows, s2cnn/soft/so3_fft.py:437)."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(9)
+    stream = torch.cuda.current_stream().cuda_stream if dev.type == "cuda" else None
+    for b_in, b_out in [(3, 5), (5, 3), (4, 4)]:
+        nb = 3
+        s = torch.randn(n3(b_in), nb, 2, generator=gen).to(dev)
+        y = torch.full((nb, 2 * b_out, 2 * b_out, 2 * b_out), float("nan"), device=dev)
+        ws = torch.empty(ops.lib.s2c_so3_fft_workspace(nb, b_in, b_out), dtype=torch.uint8, device=dev)
+        ops.lib.call("s2c_so3_rifft", s.data_ptr(), y.data_ptr(), nb, b_in, b_out, 0, None, 0,
+                     ws.data_ptr(), ws.numel(), stream)
+        assert not torch.isnan(y).any()
+        x = torch.randn(nb, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen).to(dev)
+        o = torch.full((n3(b_out), nb, 2), float("nan"), device=dev)
+        ops.lib.call("s2c_so3_rfft", x.data_ptr(), o.data_ptr(), nb, b_in, b_out, 0,
+                     ws.data_ptr(), ws.numel(), stream)
+        assert not torch.isnan(o).any()
