@@ -469,13 +469,13 @@ def run_ours(args):
     }
     if rank == 0:
         line["clocks"] = clocks
-        if world == 1:
+        if world == 1 and not args.skip_cpu:
             v, best = cpu_baseline(B)
             line["cpu_baseline"] = {"value": v, "unit": "samples/s",
                                     "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": "full batch of %d, best of 3 (%.2f s each)" % (B, best)}
-            if not args.skip_fft64:
-                line["so3_fft_b64"] = so3_fft_b64(device, hbm_gbs)
+        if world == 1 and not args.skip_fft64:
+            line["so3_fft_b64"] = so3_fft_b64(device, hbm_gbs)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
@@ -489,6 +489,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-fft64", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU-baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
