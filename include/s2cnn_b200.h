@@ -86,6 +86,20 @@ int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, in
 int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                   const float* bias, int nfeature, void* workspace, size_t workspace_bytes,
                   void* stream);
+/* Same result as s2c_so3_rifft, for callers that cannot obtain device memory at call time (a
+ * process whose GPU memory is wholly pre-reserved by another allocator, or a loop that must avoid
+ * the device-wide synchronisation of cudaMalloc/cudaFree): no workspace argument and no device
+ * allocation inside.  Scratch and tables live in two static device arrays that every GPU loading
+ * the library holds until exit (32 MiB + 4 MiB).  A call whose scratch need
+ * (s2c_so3_fft_workspace_min(b_in, b_out) * nbatch) exceeds s2c_so3_rifft_static_max_bytes(), or
+ * whose tables exceed 4 MiB, is rejected with an error.  The first call on a device, and any call
+ * that changes (b_in, b_out, for_grad), looks up the arrays' device addresses and uploads tables
+ * synchronously: issue it before any stream capture.  All calls on a device share the arrays, so
+ * calls that overlap on the GPU (other streams or threads) race; nothing has to be cleared between
+ * calls.  This entry point has no counterpart in the reference. */
+int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int b_out,
+                         int for_grad, const float* bias, int nfeature, void* stream);
+size_t s2c_so3_rifft_static_max_bytes(void);
 /* x [nspec(b_in), nbatch, 2] -> out [nbatch, 2b_out, 2b_out, 2b_out, 2] complex.
  * Replaces so3_ifft, s2cnn/soft/so3_fft.py:115-155. */
 int s2c_so3_ifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,

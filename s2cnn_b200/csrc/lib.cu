@@ -533,4 +533,183 @@ int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n
   return S2C_LAUNCH(so3_integrate_bwd, blocks, 256, 0, as_stream(st), p);
 }
 
+
+}  // extern "C"
+
+// ================================================================================================
+// s2c_so3_rifft_static: the SO(3) synthesis without any device allocation.
+//
+// Some callers of this library cannot obtain device memory at call time: a serving process whose
+// whole GPU is pre-reserved by another allocator at start-up (a later cudaMalloc simply fails), or
+// a control loop that must not take the device-wide synchronisation a cudaMalloc/cudaFree implies.
+// For them the scratch arrays of the synthesis and the constant tables it reads live in the two
+// file-scope device arrays below, which every GPU that loads this library holds until the process
+// exits (kStaticScratchBytes + kStaticTableBytes = 36 MiB per GPU).
+//
+// In host code the array names are host-side stand-ins, not device addresses; the device address
+// is fetched once per device with cudaGetSymbolAddress (with that device current) and handed to
+// the kernels.  That set-up, and the (synchronous) upload of the tables for the requested
+// bandwidths, happen on the first call on a device and again whenever a call asks for different
+// bandwidths / weighting than the tables currently held - make such a call before any stream
+// capture.  All calls on a device share the arrays: the scratch keeps the previous call's
+// contents (every element a pass reads has been written by the pass before it in the same call,
+// so nothing needs clearing), and two calls that overlap on the GPU - different streams or host
+// threads - race on it.
+// ================================================================================================
+namespace s2c {
+
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
+constexpr size_t kStaticTableBytes = (size_t)4 << 20;
+
+#ifndef S2C_EMUL
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
+#else
+alignas(256) static unsigned char g_static_scratch[kStaticScratchBytes];
+alignas(256) static unsigned char g_static_tables[kStaticTableBytes];
+#endif
+
+struct StaticDeviceState {
+  bool ready = false;
+  unsigned char* scratch = nullptr;  // device addresses of the two arrays on this device
+  unsigned char* tables = nullptr;
+  int b_beta = -1, K = -1, weighted = -1;  // configuration the table array currently holds
+  FftDev fft;
+  PanelsDev pan;
+};
+
+static std::mutex g_static_mu;
+static std::map<int, StaticDeviceState> g_static_state;
+
+static int static_setup(StaticDeviceState& st) {
+  if (st.ready) return S2C_OK;
+#ifndef S2C_EMUL
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+  if (e != cudaSuccess) return cuda_check(e, "cudaGetSymbolAddress(scratch)");
+  st.scratch = (unsigned char*)p;
+  e = cudaGetSymbolAddress(&p, g_static_tables);
+  if (e != cudaSuccess) return cuda_check(e, "cudaGetSymbolAddress(tables)");
+  st.tables = (unsigned char*)p;
+#else
+  st.scratch = g_static_scratch;
+  st.tables = g_static_tables;
+#endif
+  st.ready = true;
+  return S2C_OK;
+}
+
+// Builds the FFT and Wigner tables for (b_beta, K, weighted) on the host and copies them into the
+// static table array (no allocation; cudaMemcpy waits for the copy).
+static int static_load_tables(StaticDeviceState& st, int b_beta, int K, bool weighted,
+                              stream_t stream) {
+  if (st.b_beta == b_beta && st.K == K && st.weighted == (int)weighted) return S2C_OK;
+  const int N = 2 * b_beta;
+  FftDev f;
+  if (!fft_plan(N, f.desc))
+    return fail(S2C_ERR_UNSUPPORTED, "s2c_so3_rifft_static: unsupported FFT length");
+  std::vector<float> tw;
+  std::vector<unsigned short> pos;
+  fft_twiddles(N, tw);
+  fft_positions(f.desc, pos);
+  std::vector<float> pdata;
+  std::vector<long long> poff;
+  TableCache::build_panels(b_beta, K, K, weighted, false, pdata, poff);
+  const size_t o_tw = 0;
+  const size_t o_pos = align_up(o_tw + tw.size() * sizeof(float), 256);
+  const size_t o_off = align_up(o_pos + pos.size() * sizeof(unsigned short), 256);
+  const size_t o_dat = align_up(o_off + poff.size() * sizeof(long long), 256);
+  const size_t total = o_dat + pdata.size() * sizeof(float);
+  if (total > kStaticTableBytes)
+    return fail(S2C_ERR_UNSUPPORTED,
+                "s2c_so3_rifft_static: tables for these bandwidths need " + std::to_string(total) +
+                    " bytes, the static table array holds " + std::to_string(kStaticTableBytes));
+#ifndef S2C_EMUL
+  // kernels of an earlier call on this stream may still be reading the old tables
+  S2C_TRY(cuda_check(cudaStreamSynchronize(stream), "stream sync before table reload"));
+#endif
+  (void)stream;
+  S2C_TRY(dev_upload(st.tables + o_tw, tw.data(), tw.size() * sizeof(float)));
+  S2C_TRY(dev_upload(st.tables + o_pos, pos.data(), pos.size() * sizeof(unsigned short)));
+  S2C_TRY(dev_upload(st.tables + o_off, poff.data(), poff.size() * sizeof(long long)));
+  S2C_TRY(dev_upload(st.tables + o_dat, pdata.data(), pdata.size() * sizeof(float)));
+  f.tw = (const float2*)(st.tables + o_tw);
+  f.pos = (const unsigned short*)(st.tables + o_pos);
+  st.fft = f;
+  st.pan.nbeta = N;
+  st.pan.nl = K;
+  st.pan.K = K;
+  st.pan.npairs = (int)poff.size() - 1;
+  st.pan.s2 = 0;
+  st.pan.off = (const long long*)(st.tables + o_off);
+  st.pan.data = (const float*)(st.tables + o_dat);
+  st.b_beta = b_beta;
+  st.K = K;
+  st.weighted = (int)weighted;
+  return S2C_OK;
+}
+
+}  // namespace s2c
+
+extern "C" {
+
+size_t s2c_so3_rifft_static_max_bytes(void) { return kStaticScratchBytes; }
+
+int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int b_out,
+                         int for_grad, const float* bias, int nfeature, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_static: bad argument");
+  if (bias && nfeature < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_static: nfeature must be >= 1 with a bias");
+  const int N = 2 * b_out, K = std::min(b_in, b_out);
+  const size_t need = so3_ws_per_z(N, K) * (size_t)nbatch;
+  if (need > kStaticScratchBytes)
+    return fail(S2C_ERR_WORKSPACE,
+                "s2c_so3_rifft_static: this call needs " + std::to_string(need) +
+                    " bytes of scratch, the static array holds " +
+                    std::to_string(kStaticScratchBytes) + " (use s2c_so3_rifft with a workspace)");
+  stream_t st = as_stream(stream);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticDeviceState& dev = g_static_state[dev_current()];
+  S2C_TRY(static_setup(dev));
+  S2C_TRY(static_load_tables(dev, b_out, K, for_grad != 0, st));
+
+  const int G = fft_group(N);
+  const size_t fft_smem = fft_smem_bytes(N, G);
+  float2* t = (float2*)dev.scratch;                   // [z][K][N][N]
+  float2* s = t + (size_t)nbatch * K * N * N;         // [K][2K-1][z][N]
+  InvWignerParams w;
+  w.x = (const float2*)x;
+  w.x_zstride = nbatch;
+  w.s = s;
+  w.pan = dev.pan;
+  w.nbatch = (int)nbatch; w.N = N; w.K = K;
+  w.ZT = (int)std::min<long>(32, nbatch);
+  w.nzt = (int)((nbatch + w.ZT - 1) / w.ZT);
+  w.mode = kSo3Real;
+  const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
+  S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)dev.pan.npairs * w.nzt, kThreads, wsm, st, w));
+  InvAlphaParams a;
+  a.s = s;
+  a.out = (float*)t;
+  a.out_real = 0;
+  a.herm_n0 = 1;
+  a.nbatch = (int)nbatch; a.N = N; a.K = K; a.Kn = K; a.G = G;
+  a.nrows = nbatch * K * N;
+  a.fft = dev.fft;
+  S2C_TRY(S2C_LAUNCH(so3_inv_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem, st, a));
+  InvGammaParams g;
+  g.t = t;
+  g.out = out;
+  g.out_stride = 1;
+  g.out_off = 0;
+  g.bias = bias;
+  g.nfeat = nfeature > 0 ? nfeature : 1;
+  g.z0 = 0;
+  g.N = N; g.b = b_out; g.K = K; g.G = G;
+  g.npairs = nbatch * N * b_out;
+  g.fft = dev.fft;
+  return S2C_LAUNCH(so3_inv_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g);
+}
+
 }  // extern "C"
