@@ -74,6 +74,15 @@ size_t s2c_so3_fft_workspace_min(int b_in, int b_out);
  * Replaces so3_rfft, s2cnn/soft/so3_fft.py:64-112 (+ kernel so3fft.cu :246-350, REAL_IN). */
 int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* s2c_so3_rfft of max(x, 0): the ReLU that precedes an SO3Convolution in the reference's models
+ * (e.g. examples/mnist/run.py:88-93) applied while the signal is read, so the activated tensor
+ * never exists in memory.  Only for 2 b_in <= 32 (single-kernel path); other sizes return
+ * "unsupported". */
+int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_out,
+                      void* workspace, size_t workspace_bytes, void* stream);
+/* Test switch (no counterpart in the reference): non-zero routes small bandwidths through the
+ * general three-pass kernels instead of the single-kernel path, so both can be checked. */
+void s2c_debug_force_general_path(int on);
 /* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].
  * Replaces so3_fft, s2cnn/soft/so3_fft.py:12-61. */
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
@@ -124,6 +133,10 @@ int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_
  * Replaces so3_mm / _cuda_SO3_mm.forward, s2cnn/so3_mm.py:8-93. */
 int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nbatch, int f_in, int f_out,
                void* stream);
+/* Synchronises the device and returns 0 if no tensor-core so3_mm launch has reported a barrier
+ * time-out since the library was loaded, 1 if one has, -1 on a CUDA error (no counterpart in the
+ * reference). */
+int s2c_so3_mm_tc_status(void);
 /* gx = d/dx: replaces _cuda_SO3_mm.backward (grad-x instantiation), s2cnn/so3_mm.py:108-113. */
 int s2c_so3_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nbatch, int f_in,
                      int f_out, void* stream);

@@ -35,6 +35,8 @@ _SIGNATURES = {
     "s2c_so3_fft_workspace": (c_size_t, [c_long, c_int, c_int]),
     "s2c_so3_fft_workspace_min": (c_size_t, [c_int, c_int]),
     "s2c_so3_rfft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
+    "s2c_so3_rfft_relu": (c_int, [_P, _P, c_long, c_int, c_int, _P, c_size_t, _P]),
+    "s2c_debug_force_general_path": (None, [c_int]),
     "s2c_so3_fft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
     "s2c_so3_rifft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P, c_size_t, _P]),
     "s2c_so3_rifft_static": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P]),
@@ -44,6 +46,7 @@ _SIGNATURES = {
     "s2c_s2_fft": (c_int, [_P, c_int, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
     "s2c_s2_ifft": (c_int, [_P, _P, c_int, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
     "s2c_so3_mm": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "s2c_so3_mm_tc_status": (c_int, []),
     "s2c_so3_mm_gradx": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "s2c_so3_mm_grady": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "s2c_s2_mm": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),

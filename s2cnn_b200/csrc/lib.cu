@@ -11,11 +11,14 @@
 #include "tables.h"
 #include "fft_device.h"
 #include "so3_kernels.h"
+#include "so3_fused_kernels.h"
 #include "cgemm_kernels.h"
+#include "so3_mm_tc.h"
 #include "misc_kernels.h"
 
 namespace s2c {
 thread_local long g_launch_count = 0;
+static bool g_force_general = false;  // test switch: route small bandwidths through the general path
 
 #define S2C_TRY(expr)            \
   do {                           \
@@ -43,19 +46,34 @@ static int check_b(int b_in, int b_out) {
 // ---------------------------------------------------------------------------------------------
 static int so3_analysis(const float* x, long in_stride, long in_off, float2* out, long nbatch,
                         int b_in, int b_out, bool weighted, int mode, void* ws, size_t ws_bytes,
-                        stream_t st) {
+                        stream_t st, bool relu = false) {
   const int N = 2 * b_in, K = std::min(b_in, b_out);
   FftDev fft;
   PanelsDev pan;
   S2C_TRY(TableCache::get().fft(N, fft));
   S2C_TRY(TableCache::get().panels(b_in, b_out, K, weighted, false, pan));
+  if (b_out > b_in && mode == kSo3Real)  // rows with |m| or |n| >= b_in stay zero (so3_fft.py:44-48)
+    S2C_TRY(dev_memset_async(out, 0, (size_t)so3_nspec(b_out) * nbatch * sizeof(float2), st));
+  if (!g_force_general && N <= kFusedMaxN &&
+      fused_smem_bytes(N, pan.nrows) <= (size_t)dev_smem_limit() - 1024) {
+    FwdFusedParams f;
+    f.x = x; f.in_stride = in_stride; f.in_off = in_off;
+    f.out = out; f.out_zstride = nbatch;
+    f.pan = pan; f.tw = fft.tw;
+    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N);
+    f.nrows = pan.nrows; f.mode = mode; f.relu = relu;
+    int rc = S2C_OK;
+    const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
+    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_fwd_fused, kN, grid, 256,
+                                        fused_smem_bytes(N, pan.nrows), st, f));
+    return rc;
+  }
+  if (relu) return fail(S2C_ERR_UNSUPPORTED, "fused ReLU input needs the small-bandwidth path");
   const size_t per_z = so3_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || ws == nullptr)
     return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" +
                                        std::to_string(per_z) + " bytes needed)");
-  if (b_out > b_in && mode == kSo3Real)  // rows with |m| or |n| >= b_in stay zero (so3_fft.py:44-48)
-    S2C_TRY(dev_memset_async(out, 0, (size_t)so3_nspec(b_out) * nbatch * sizeof(float2), st));
   const int G = fft_group(N);
   const size_t fft_smem = fft_smem_bytes(N, G);
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
@@ -106,6 +124,21 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
   PanelsDev pan;
   S2C_TRY(TableCache::get().fft(N, fft));
   S2C_TRY(TableCache::get().panels(b_out, K, K, weighted, false, pan));
+  if (!g_force_general && N <= kFusedMaxN &&
+      fused_smem_bytes(N, pan.nrows) <= (size_t)dev_smem_limit() - 1024) {
+    InvFusedParams f;
+    f.x = x; f.x_zstride = nbatch;
+    f.out = out; f.out_stride = out_stride; f.out_off = out_off;
+    f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1;
+    f.pan = pan; f.tw = fft.tw;
+    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N);
+    f.nrows = pan.nrows; f.mode = mode;
+    int rc = S2C_OK;
+    const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
+    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_inv_fused, kN, grid, 256,
+                                        fused_smem_bytes(N, pan.nrows), st, f));
+    return rc;
+  }
   const size_t per_z = so3_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || ws == nullptr)
@@ -338,6 +371,16 @@ int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, i
                       ws_bytes, as_stream(stream));
 }
 
+int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_out, void* ws,
+                      size_t ws_bytes, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rfft_relu: bad argument");
+  return so3_analysis(x, 1, 0, (float2*)out, nbatch, b_in, b_out, true, kSo3Real, ws, ws_bytes,
+                      as_stream(stream), true);
+}
+
+void s2c_debug_force_general_path(int on) { g_force_general = on != 0; }
+
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                 void* ws, size_t ws_bytes, void* stream) {
   S2C_TRY(check_b(b_in, b_out));
@@ -458,9 +501,39 @@ int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_
 }
 
 // ---- spectral products ---------------------------------------------------------------------------
+#ifndef S2C_EMUL
+static __device__ int g_tc_err_flag;
+#endif
+
 int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, int fo, void* st) {
   if (!x || !y || !z) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm: null pointer");
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+#ifndef S2C_EMUL
+  if (!g_force_general && so3_mm_tc_supported(nl, nb, fi, fo)) {
+    MmTcParams p;
+    p.x = x; p.y = y; p.z = z;
+    p.nl = nl; p.nb = nb; p.fi = fi; p.fo = fo;
+    const int fi2 = 2 * fi;
+    if (fi2 <= kTcKMax) { p.kblk = (fi2 + 7) / 8 * 8; p.nblk = 1; }
+    else { p.kblk = kTcKMax; p.nblk = (fi2 + kTcKMax - 1) / kTcKMax; }
+    void* flag = nullptr;
+    S2C_TRY(cuda_check(cudaGetSymbolAddress(&flag, g_tc_err_flag), "tensor-core status flag"));
+    p.err = (int*)flag;
+    return launch_impl(so3_mm_tc_kernel, "so3_mm_tc_kernel", so3_mm_tc_tiles(nl, nb, fo),
+                       kTcThreads, kTcSmemBytes, as_stream(st), p);
+  }
+#endif
   return mm_dispatch(true, kMmFwd, x, y, z, nl, nb, fi, fo, as_stream(st));
+}
+
+int s2c_so3_mm_tc_status(void) {
+#ifndef S2C_EMUL
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_err_flag, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+#else
+  return 0;
+#endif
 }
 int s2c_so3_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nb, int fi, int fo,
                      void* st) {
@@ -641,6 +714,8 @@ static int static_load_tables(StaticDeviceState& st, int b_beta, int K, bool wei
   st.pan.K = K;
   st.pan.npairs = (int)poff.size() - 1;
   st.pan.s2 = 0;
+  st.pan.nrows = (int)(poff.back() / N);
+  st.pan.rowmap = nullptr;
   st.pan.off = (const long long*)(st.tables + o_off);
   st.pan.data = (const float*)(st.tables + o_dat);
   st.b_beta = b_beta;

@@ -37,8 +37,10 @@ struct PanelsDev {
   int K;       // frequencies |m|, n < K
   int npairs;
   int s2;      // 1: S2 panels (n = 0, all m), 0: SO(3) half plane
+  int nrows;   // total panel rows = off[npairs] / nbeta
   const float* data;        // device
   const long long* off;     // device, npairs + 1 offsets (in floats)
+  const int* rowmap;        // device, nrows entries: l | (m + 128) << 8 | n << 16 of each panel row
 };
 
 S2C_HD int so3_npairs(int K) { return K + (K - 1) * (2 * K - 1); }
@@ -122,6 +124,18 @@ class TableCache {
     }
   }
 
+  // (l, m, n) of every panel row, in panel order.
+  static void build_rowmap(int nl, int K, bool s2, std::vector<int>& rowmap) {
+    const int npairs = s2 ? 2 * K - 1 : so3_npairs(K);
+    rowmap.clear();
+    for (int p = 0; p < npairs; ++p) {
+      int m, n;
+      if (s2) { m = p - (K - 1); n = 0; } else so3_pair_decode(p, K, m, n);
+      const int lmin = std::max(std::abs(m), n);
+      for (int l = lmin; l < nl; ++l) rowmap.push_back(l | ((m + 128) << 8) | (n << 16));
+    }
+  }
+
   int panels(int b_beta, int nl, int K, bool weighted, bool s2, PanelsDev& out) {
     std::lock_guard<std::mutex> g(mu_);
     const int dev = dev_current();
@@ -131,14 +145,21 @@ class TableCache {
       std::vector<float> data;
       std::vector<long long> off;
       build_panels(b_beta, nl, K, weighted, s2, data, off);
+      std::vector<int> rowmap;
+      build_rowmap(nl, K, s2, rowmap);
       void* dd = dev_alloc(data.size() * sizeof(float));
       void* doff = dev_alloc(off.size() * sizeof(long long));
-      if (!dd || !doff) return fail(S2C_ERR_CUDA, "table allocation failed");
+      void* drm = dev_alloc(rowmap.size() * sizeof(int));
+      if (!dd || !doff || !drm) return fail(S2C_ERR_CUDA, "table allocation failed");
       int rc = dev_upload(dd, data.data(), data.size() * sizeof(float));
       if (rc) return rc;
       rc = dev_upload(doff, off.data(), off.size() * sizeof(long long));
       if (rc) return rc;
+      rc = dev_upload(drm, rowmap.data(), rowmap.size() * sizeof(int));
+      if (rc) return rc;
       PanelsDev pd;
+      pd.nrows = (int)rowmap.size();
+      pd.rowmap = (const int*)drm;
       pd.nbeta = 2 * b_beta;
       pd.nl = nl;
       pd.K = K;
@@ -174,16 +195,15 @@ class TableCache {
   void clear() {
     std::lock_guard<std::mutex> g(mu_);
     for (auto& kv : fft_) { dev_free((void*)kv.second.tw); dev_free((void*)kv.second.pos); }
-    for (auto& kv : panels_) { dev_free((void*)kv.second.data); dev_free((void*)kv.second.off); }
+    for (auto& kv : panels_) {
+      dev_free((void*)kv.second.data);
+      dev_free((void*)kv.second.off);
+      dev_free((void*)kv.second.rowmap);
+    }
     for (auto& kv : quad_) dev_free((void*)kv.second);
     fft_.clear();
     panels_.clear();
     quad_.clear();
-  }
-
-  size_t bytes_cached() {
-    std::lock_guard<std::mutex> g(mu_);
-    return 0;
   }
 
  private:

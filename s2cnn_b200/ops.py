@@ -56,8 +56,9 @@ class Ops:
         return torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=like.device)
 
     # -- SO(3) transforms ----------------------------------------------------------------------
-    def so3_rfft(self, x, for_grad=False, b_out=None):
-        """[..., 2b, 2b, 2b] real -> [nspec(b_out), ..., 2]"""
+    def so3_rfft(self, x, for_grad=False, b_out=None, relu=False):
+        """[..., 2b, 2b, 2b] real -> [nspec(b_out), ..., 2]; with ``relu`` the transform of
+        max(x, 0) (activation applied while reading; small bandwidths, forward weighting only)."""
         self._prep(x)
         b_in = x.size(-1) // 2
         assert x.size(-1) == 2 * b_in and x.size(-2) == 2 * b_in and x.size(-3) == 2 * b_in
@@ -68,8 +69,13 @@ class Ops:
         out = x.new_empty((so3_nspec(b_out), nbatch, 2))
         with self._ctx(x):
             ws = self._ws(self.lib.s2c_so3_fft_workspace(nbatch, b_in, b_out), x)
-            self.lib.call("s2c_so3_rfft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
-                          int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+            if relu:
+                assert not for_grad
+                self.lib.call("s2c_so3_rfft_relu", x.data_ptr(), out.data_ptr(), nbatch, b_in,
+                              b_out, ws.data_ptr(), ws.numel(), self._stream(x))
+            else:
+                self.lib.call("s2c_so3_rfft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
+                              int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
         return out.view(-1, *lead, 2)
 
     def so3_fft(self, x, for_grad=False, b_out=None):

@@ -219,3 +219,43 @@ def test_write_coverage_no_stale_values(backend):
         ops.lib.call("s2c_so3_rfft", x.data_ptr(), o.data_ptr(), nb, b_in, b_out, 0,
                      ws.data_ptr(), ws.numel(), stream)
         assert not torch.isnan(o).any()
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("name", ["so3_fft_7_5", "so3_fft_4_7", "so3_fft_6_6", "so3_fft_10_11"])
+def test_general_three_pass_path_forced(backend, name):
+    """Bandwidths up to 16 normally take the single-kernel path; the switch routes them through the
+    general three-pass kernels (the path every larger bandwidth uses) so both stay covered."""
+    ops, dev = backends.get(backend)
+    g = golden(name)
+    b_out = int(g["b_out"])
+    ops.lib.s2c_debug_force_general_path(1)
+    try:
+        for fg in (False, True):
+            t = "_grad" if fg else ""
+            assert_close(ops.so3_rfft(g["x_real"].to(dev), fg, b_out), g["rfft" + t], name + " rfft" + t)
+            assert_close(ops.so3_fft(g["x_complex"].to(dev), fg, b_out), g["fft" + t], name + " fft" + t)
+            assert_close(ops.so3_ifft(g["spectrum"].to(dev), fg, b_out), g["ifft" + t], name + " ifft" + t)
+            assert_close(ops.so3_rifft(g["spectrum"].to(dev), fg, b_out), g["rifft" + t], name + " rifft" + t)
+    finally:
+        ops.lib.s2c_debug_force_general_path(0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(17, 17, 2), (20, 8, 3), (9, 18, 1)])
+def test_large_bandwidth_general_path(backend, b_in, b_out, nbatch):
+    """2b > 32: the general path on its own (FFT lengths 34 = 2*17, 40, 36)."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in)
+    x = torch.randn(nbatch, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen)
+    s = torch.randn(n3(b_in), nbatch, 2, generator=gen)
+    assert_close(ops.so3_rfft(x.to(dev), False, b_out), O.so3_rfft(x, False, b_out), "rfft")
+    assert_close(ops.so3_rifft(s.to(dev), False, b_out), O.so3_rifft(s, False, b_out), "rifft")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_rfft_with_relu_on_load(backend):
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(12)
+    x = torch.randn(5, 12, 12, 12, generator=gen)
+    assert_close(ops.so3_rfft(x.to(dev), b_out=4, relu=True), O.so3_rfft(torch.relu(x), b_out=4), "relu rfft")
