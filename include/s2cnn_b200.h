@@ -109,6 +109,15 @@ int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, 
 int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int b_out,
                          int for_grad, const float* bias, int nfeature, void* stream);
 size_t s2c_so3_rifft_static_max_bytes(void);
+/* The tail of S2Convolution.forward in one call (s2cnn/soft/s2_conv.py:42-45):
+ *   out = so3_rifft(s2_mm(xs, ys)) + bias
+ * xs [b*b, nbatch, f_in, 2], ys [b*b, f_in, f_out, 2], out [nbatch, f_out, 2b, 2b, 2b], bias [f_out]
+ * or NULL.  For 2b <= 32 the product is evaluated inside the synthesis kernel and the SO(3)
+ * spectrum is never written to memory; larger b run the two steps through the workspace. */
+size_t s2c_s2_conv_synthesis_workspace(int nbatch, int f_out, int b);
+int s2c_s2_conv_synthesis(const float* xs, const float* ys, float* out, int nbatch, int f_in,
+                          int f_out, int b, const float* bias, void* workspace,
+                          size_t workspace_bytes, void* stream);
 /* x [nspec(b_in), nbatch, 2] -> out [nbatch, 2b_out, 2b_out, 2b_out, 2] complex.
  * Replaces so3_ifft, s2cnn/soft/so3_fft.py:115-155. */
 int s2c_so3_ifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,

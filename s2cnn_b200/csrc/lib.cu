@@ -116,9 +116,23 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
 // ---------------------------------------------------------------------------------------------
 // SO(3) synthesis:  spectrum rows [nspec(b_in)][nbatch] -> real signal (strided)
 // ---------------------------------------------------------------------------------------------
+struct S2ProductArgs {
+  const float2* xs = nullptr;
+  const float2* ys = nullptr;
+  int nb = 0, fin = 0, fout = 0;
+};
+
+static bool so3_synthesis_is_fused(int b_in, int b_out) {
+  const int N = 2 * b_out, K = std::min(b_in, b_out);
+  if (g_force_general || N > kFusedMaxN) return false;
+  const int nrows = (so3_nspec(K) - K) / 2 + K;  // half-plane rows: the (0,0) pair is its own mirror
+  return fused_smem_bytes(N, nrows) <= (size_t)dev_smem_limit() - 1024;
+}
+
 static int so3_synthesis(const float2* x, float* out, long out_stride, long out_off, long nbatch,
                          int b_in, int b_out, bool weighted, int mode, const float* bias,
-                         int nfeat, void* ws, size_t ws_bytes, stream_t st) {
+                         int nfeat, void* ws, size_t ws_bytes, stream_t st,
+                         const S2ProductArgs* prod = nullptr) {
   const int N = 2 * b_out, K = std::min(b_in, b_out);
   FftDev fft;
   PanelsDev pan;
@@ -133,6 +147,12 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     f.pan = pan; f.tw = fft.tw;
     f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N);
     f.nrows = pan.nrows; f.mode = mode;
+    f.xs = nullptr; f.ys = nullptr; f.s2_nb = f.s2_fin = f.s2_fout = 0;
+    if (prod) {
+      f.mode = kS2Product;
+      f.xs = prod->xs; f.ys = prod->ys;
+      f.s2_nb = prod->nb; f.s2_fin = prod->fin; f.s2_fout = prod->fout;
+    }
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
     S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_inv_fused, kN, grid, 256,
@@ -399,6 +419,35 @@ int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, 
   if (bias && nfeature < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft: nfeature must be >= 1 with a bias");
   return so3_synthesis((const float2*)x, out, 1, 0, nbatch, b_in, b_out, for_grad != 0, kSo3Real,
                        bias, nfeature, ws, ws_bytes, as_stream(stream));
+}
+
+size_t s2c_s2_conv_synthesis_workspace(int nbatch, int f_out, int b) {
+  if (so3_synthesis_is_fused(b, b)) return 16;
+  const size_t z_bytes = (size_t)so3_nspec(b) * nbatch * f_out * sizeof(float2);
+  return z_bytes + s2c_so3_fft_workspace((long)nbatch * f_out, b, b);
+}
+
+int s2c_s2_conv_synthesis(const float* xs, const float* ys, float* out, int nbatch, int f_in,
+                          int f_out, int b, const float* bias, void* ws, size_t ws_bytes,
+                          void* stream) {
+  S2C_TRY(check_b(b, b));
+  if (!xs || !ys || !out || nbatch < 1 || f_in < 1 || f_out < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_s2_conv_synthesis: bad argument");
+  const long nz = (long)nbatch * f_out;
+  if (so3_synthesis_is_fused(b, b)) {
+    S2ProductArgs pr;
+    pr.xs = (const float2*)xs; pr.ys = (const float2*)ys;
+    pr.nb = nbatch; pr.fin = f_in; pr.fout = f_out;
+    return so3_synthesis(nullptr, out, 1, 0, nz, b, b, false, kSo3Real, bias, f_out, ws, ws_bytes,
+                         as_stream(stream), &pr);
+  }
+  // larger bandwidths: product into the head of the workspace, then the general synthesis
+  const size_t z_bytes = (size_t)so3_nspec(b) * nz * sizeof(float2);
+  if (!ws || ws_bytes <= z_bytes)
+    return fail(S2C_ERR_WORKSPACE, "s2c_s2_conv_synthesis: workspace too small");
+  S2C_TRY(mm_dispatch(false, kMmFwd, xs, ys, (float*)ws, b, nbatch, f_in, f_out, as_stream(stream)));
+  return so3_synthesis((const float2*)ws, out, 1, 0, nz, b, b, false, kSo3Real, bias, f_out,
+                       (unsigned char*)ws + z_bytes, ws_bytes - z_bytes, as_stream(stream));
 }
 
 int s2c_so3_ifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,

@@ -51,7 +51,26 @@ struct InvFusedParams {
   PanelsDev pan;       // beta grid of b_out, nl = K
   const float2* tw;    // N twiddles
   int nbatch, K, BG, KP, nrows, mode;
+  // mode == kS2Product: the spectrum is never materialised; row (l,m,n), batch z = (i, j) is
+  //   sum_k xs[l,m,i,k] conj(ys[l,n,k,j])        (s2_mm fused into the synthesis prologue)
+  const float2* xs;    // [K*K, s2_nb, s2_fin]
+  const float2* ys;    // [K*K, s2_fin, s2_fout]
+  int s2_nb, s2_fin, s2_fout;
 };
+
+S2C_D float2 s2_product_entry(const InvFusedParams& p, int l, int m, int n, int i, int j) {
+  const float2* xr = p.xs + ((long)(l * l + l + m) * p.s2_nb + i) * p.s2_fin;
+  const float2* yr = p.ys + (long)(l * l + l + n) * p.s2_fin * p.s2_fout + j;
+  float re = 0.f, im = 0.f;
+  for (int k = 0; k < p.s2_fin; ++k) {
+    const float2 a = xr[k], b = yr[(long)k * p.s2_fout];
+    re = fmaf(a.x, b.x, re);
+    re = fmaf(a.y, b.y, re);
+    im = fmaf(a.y, b.x, im);
+    im = fmaf(-a.x, b.y, im);
+  }
+  return make_float2(re, im);
+}
 
 template <int N>
 struct so3_inv_fused_impl {
@@ -72,8 +91,16 @@ struct so3_inv_fused_impl {
       if (zz < zc) {
         int l, m, n;
         rowmap_unpack(p.pan.rowmap[r], l, m, n);
-        float2 a = p.x[so3_row(l, m, n) * p.x_zstride + z0 + zz];
-        float2 b = p.x[so3_row(l, -m, -n) * p.x_zstride + z0 + zz];
+        float2 a, b;
+        if (p.mode == kS2Product) {
+          const int z = (int)(z0 + zz);
+          const int i = z / p.s2_fout, j = z - i * p.s2_fout;
+          a = s2_product_entry(p, l, m, n, i, j);
+          b = s2_product_entry(p, l, -m, -n, i, j);
+        } else {
+          a = p.x[so3_row(l, m, n) * p.x_zstride + z0 + zz];
+          b = p.x[so3_row(l, -m, -n) * p.x_zstride + z0 + zz];
+        }
         if (p.mode == kSo3RotI) {
           a = make_float2(a.y, -a.x);
           b = make_float2(b.y, -b.x);

@@ -153,6 +153,7 @@ enum WignerMode : int {
   kSo3AccumI = 1,    // X += i * result (imaginary part of a complex input), mirror likewise
   kS2 = 2,           // S2 transform: rows l^2 + l + m, no mirror
   kSo3RotI = 3,      // synthesis only: spectrum multiplied by -i first (imaginary output part)
+  kS2Product = 4,    // fused synthesis only: spectrum = s2_mm(xs, ys) computed on the fly
 };
 
 struct FwdWignerParams {

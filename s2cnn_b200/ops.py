@@ -121,6 +121,31 @@ class Ops:
                           self._stream(x))
         return out.view(*lead, n, n, n)
 
+    def s2_conv_synthesis(self, xs, ys, bias=None):
+        """so3_rifft(s2_mm(xs, ys)) + bias without materialising the SO(3) spectrum (small b).
+        xs [b^2, batch, f_in, 2], ys [b^2, f_in, f_out, 2] -> [batch, f_out, 2b, 2b, 2b]"""
+        self._prep(xs, ys, bias)
+        nspec, nbatch, f_in, two = xs.shape
+        assert two == 2 and ys.size(0) == nspec and ys.size(1) == f_in and ys.size(3) == 2
+        f_out = ys.size(2)
+        b = round(nspec ** 0.5)
+        assert nspec == b * b
+        xs = xs.contiguous()
+        ys = ys.contiguous()
+        n = 2 * b
+        out = xs.new_empty((nbatch, f_out, n, n, n))
+        bias_ptr = None
+        if bias is not None:
+            bias = bias.contiguous().view(-1)
+            assert bias.numel() == f_out
+            bias_ptr = bias.data_ptr()
+        with self._ctx(xs):
+            ws = self._ws(self.lib.s2c_s2_conv_synthesis_workspace(nbatch, f_out, b), xs)
+            self.lib.call("s2c_s2_conv_synthesis", xs.data_ptr(), ys.data_ptr(), out.data_ptr(),
+                          nbatch, f_in, f_out, b, bias_ptr, ws.data_ptr(), ws.numel(),
+                          self._stream(xs))
+        return out
+
     def so3_ifft(self, x, for_grad=False, b_out=None):
         """[nspec(b_in), ..., 2] -> [..., 2b_out, 2b_out, 2b_out, 2] complex"""
         self._prep(x)

@@ -5,10 +5,39 @@ import torch
 from torch.nn.modules import Module
 from torch.nn.parameter import Parameter
 
+from ..ops import cuda_ops
 from ..s2_ft import s2_rft
-from ..s2_mm import s2_mm
 from .s2_fft import S2_fft_real
-from .so3_fft import SO3_ifft_real_bias
+from .so3_fft import so3_rfft
+
+
+class _S2ProductSynthesis(torch.autograd.Function):
+    """``SO3_ifft_real(s2_mm(x, y)) + bias`` (s2_conv.py:42-45) as one op: for small bandwidths the
+    product is evaluated inside the synthesis kernel and the SO(3) spectrum never reaches memory.
+    Backward is the reference's chain: so3_rfft(for_grad) of the output gradient, then the grad-x /
+    grad-y products (s2cnn/soft/so3_fft.py:467-469, s2cnn/s2_mm.py:67-101)."""
+
+    @staticmethod
+    def forward(ctx, x, y, bias):  # pylint: disable=W
+        ctx.save_for_backward(x, y)
+        ctx.bias_shape = bias.shape
+        return cuda_ops().s2_conv_synthesis(x, y, bias.reshape(-1))
+
+    @staticmethod
+    def backward(ctx, grad_output):  # pylint: disable=W
+        x, y = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        gx = gy = gb = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            b = round(x.size(0) ** 0.5)
+            gz = so3_rfft(grad_output, for_grad=True, b_out=b)  # [l * m * n, batch, f_out, complex]
+            if ctx.needs_input_grad[0]:
+                gx = cuda_ops().s2_mm_gradx(gz, y, x.size(1), x.size(2))
+            if ctx.needs_input_grad[1]:
+                gy = cuda_ops().s2_mm_grady(gz, x, y.size(2))
+        if ctx.needs_input_grad[2]:
+            gb = grad_output.sum(dim=(0, 2, 3, 4)).reshape(ctx.bias_shape)
+        return gx, gy, gb
 
 
 class S2Convolution(Module):
@@ -41,5 +70,5 @@ class S2Convolution(Module):
         assert x.size(3) == 2 * self.b_in
         x = S2_fft_real.apply(x, self.b_out)  # [l * m, batch, feature_in, complex]
         y = s2_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m, feature_in, feature_out, complex]
-        z = s2_mm(x, y)  # [l * m * n, batch, feature_out, complex]
-        return SO3_ifft_real_bias.apply(z, self.bias)  # [batch, feature_out, beta, alpha, gamma]
+        # s2_mm -> SO3_ifft_real -> + bias, fused: [batch, feature_out, beta, alpha, gamma]
+        return _S2ProductSynthesis.apply(x, y, self.bias)

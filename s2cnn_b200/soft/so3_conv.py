@@ -8,7 +8,7 @@ from torch.nn.parameter import Parameter
 
 from ..so3_ft import so3_rft
 from ..so3_mm import so3_mm
-from .so3_fft import SO3_fft_real, SO3_ifft_real_bias
+from .so3_fft import SO3_fft_real, SO3_fft_real_relu, SO3_ifft_real_bias
 
 
 class SO3Convolution(Module):
@@ -31,16 +31,22 @@ class SO3Convolution(Module):
         # the scaling stays outside the parameter (so3_conv.py:30-34)
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
 
-    def forward(self, x):  # pylint: disable=W
+    def forward(self, x, relu_input=False):  # pylint: disable=W
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
+        :relu_input: (extension) compute conv(relu(x)); the activation is applied while x is read
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
         assert x.size(1) == self.nfeature_in
         assert x.size(2) == 2 * self.b_in
         assert x.size(3) == 2 * self.b_in
         assert x.size(4) == 2 * self.b_in
-        x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
+        if relu_input and 2 * self.b_in <= 32:
+            x = SO3_fft_real_relu.apply(x, self.b_out)
+        else:
+            if relu_input:
+                x = torch.relu(x)
+            x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
         y = so3_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m * n, feature_in, feature_out, complex]
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)

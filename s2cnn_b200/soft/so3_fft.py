@@ -60,6 +60,24 @@ class SO3_fft_real(torch.autograd.Function):
         return so3_rifft(grad_output.contiguous(), for_grad=True, b_out=ctx.b_in), None
 
 
+class SO3_fft_real_relu(torch.autograd.Function):
+    """``SO3_fft_real`` of ``relu(x)`` with the activation applied while the signal is read (the
+    ReLU between two convolutions of the reference's models, e.g. examples/mnist/run.py:88-93,
+    folded into the consumer).  Needs 2 b_in <= 32."""
+
+    @staticmethod
+    def forward(ctx, x, b_out=None):  # pylint: disable=W
+        ctx.b_in = x.size(-1) // 2
+        ctx.save_for_backward(x)
+        return cuda_ops().so3_rfft(x, b_out=b_out, relu=True)
+
+    @staticmethod
+    def backward(ctx, grad_output):  # pylint: disable=W
+        (x,) = ctx.saved_tensors
+        g = so3_rifft(grad_output.contiguous(), for_grad=True, b_out=ctx.b_in)
+        return g * (x > 0).to(g.dtype), None
+
+
 class SO3_ifft_real(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, b_out=None):  # pylint: disable=W

@@ -259,3 +259,21 @@ def test_rfft_with_relu_on_load(backend):
     gen = torch.Generator().manual_seed(12)
     x = torch.randn(5, 12, 12, 12, generator=gen)
     assert_close(ops.so3_rfft(x.to(dev), b_out=4, relu=True), O.so3_rfft(torch.relu(x), b_out=4), "relu rfft")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b,nb,fi,fo", [(4, 3, 2, 3), (6, 5, 1, 4), (1, 2, 3, 2), (10, 2, 1, 6)])
+def test_s2_product_synthesis_fused(backend, b, nb, fi, fo):
+    """so3_rifft(s2_mm(x, y)) + bias in one call, single-kernel path and general path."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b * 10 + fo)
+    xs = torch.randn(b * b, nb, fi, 2, generator=gen)
+    ys = torch.randn(b * b, fi, fo, 2, generator=gen)
+    bias = torch.randn(fo, generator=gen)
+    ref = O.so3_rifft(O.s2_mm(xs, ys)) + bias.view(1, fo, 1, 1, 1)
+    assert_close(ops.s2_conv_synthesis(xs.to(dev), ys.to(dev), bias.to(dev)), ref, "fused")
+    ops.lib.s2c_debug_force_general_path(1)
+    try:
+        assert_close(ops.s2_conv_synthesis(xs.to(dev), ys.to(dev), bias.to(dev)), ref, "general")
+    finally:
+        ops.lib.s2c_debug_force_general_path(0)

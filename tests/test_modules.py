@@ -177,3 +177,27 @@ def test_small_network_matches_oracle(backend):
         assert_close(y, yo.detach(), "net out")
         assert_close(c1.kernel.grad, k1.grad, "net gk1")
         assert_close(c2.kernel.grad, k2.grad, "net gk2")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_fused_relu_variants_match_unfused(backend):
+    """conv(relu(x)) via relu_input=True and so3_relu_integrate equal the unfused composition,
+    forward and backward."""
+    import s2cnn_b200 as S
+    g3 = S.so3_near_identity_grid(max_beta=np.pi / 8, n_alpha=4, n_beta=2, n_gamma=2)
+    torch.manual_seed(5)
+    conv = S.SO3Convolution(2, 3, 4, 3, g3)
+    x0 = torch.randn(2, 2, 8, 8, 8)
+    with backends.active(backend) as (_, dev):
+        conv = conv.to(dev)
+        xa = x0.clone().to(dev).requires_grad_(True)
+        ya = S.so3_relu_integrate(conv(xa, relu_input=True))
+        ya.square().sum().backward()
+        ga, gka = xa.grad.clone(), conv.kernel.grad.clone()
+        conv.zero_grad()
+        xb = x0.clone().to(dev).requires_grad_(True)
+        yb = S.so3_integrate(torch.relu(conv(torch.relu(xb))))
+        yb.square().sum().backward()
+        assert_close(ya, yb.detach(), "fused relu fwd")
+        assert_close(ga, xb.grad, "fused relu gx")
+        assert_close(gka, conv.kernel.grad, "fused relu gk")
