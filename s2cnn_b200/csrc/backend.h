@@ -182,6 +182,10 @@ struct float2 {
 struct float4 {
   float x, y, z, w;
 };
+struct int4 {
+  int x, y, z, w;
+};
+inline int4 make_int4(int x, int y, int z, int w) { return int4{x, y, z, w}; }
 inline float2 make_float2(float x, float y) { return float2{x, y}; }
 inline float4 make_float4(float x, float y, float z, float w) { return float4{x, y, z, w}; }
 inline float __ldg(const float* p) { return *p; }

@@ -60,7 +60,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     f.x = x; f.in_stride = in_stride; f.in_off = in_off;
     f.out = out; f.out_zstride = nbatch;
     f.pan = pan; f.tw = fft.tw;
-    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N);
+    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N); f.PS = fused_plane_stride(N, K);
     f.nrows = pan.nrows; f.mode = mode; f.relu = relu;
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
@@ -145,7 +145,7 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     f.out = out; f.out_stride = out_stride; f.out_off = out_off;
     f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1;
     f.pan = pan; f.tw = fft.tw;
-    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N);
+    f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N); f.PS = fused_plane_stride(N, K);
     f.nrows = pan.nrows; f.mode = mode;
     f.xs = nullptr; f.ys = nullptr; f.s2_nb = f.s2_fin = f.s2_fout = 0;
     if (prod) {

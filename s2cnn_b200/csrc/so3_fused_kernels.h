@@ -25,14 +25,7 @@
 namespace s2c {
 
 constexpr int kFusedZG = 4;
-
-template <int I, int E, class F>
-S2C_D void static_for(F&& f) {
-  if constexpr (I < E) {
-    f(std::integral_constant<int, I>{});
-    static_for<I + 1, E>(f);
-  }
-}
+constexpr int kMaxBG = 8;   // upper bound of the betas per group (register accumulators)
 
 S2C_D void rowmap_unpack(int packed, int& l, int& m, int& n) {
   l = packed & 0xff;
@@ -50,7 +43,7 @@ struct InvFusedParams {
   int nfeat;
   PanelsDev pan;       // beta grid of b_out, nl = K
   const float2* tw;    // N twiddles
-  int nbatch, K, BG, KP, nrows, mode;
+  int nbatch, K, BG, KP, PS, nrows, mode;
   // mode == kS2Product: the spectrum is never materialised; row (l,m,n), batch z = (i, j) is
   //   sum_k xs[l,m,i,k] conj(ys[l,n,k,j])        (s2_mm fused into the synthesis prologue)
   const float2* xs;    // [K*K, s2_nb, s2_fin]
@@ -79,11 +72,19 @@ struct so3_inv_fused_impl {
     const int K = p.K, KP = p.KP;
     float2* tw = reinterpret_cast<float2*>(smem);
     float2* Xh = tw + N;                              // [nrows][ZG]
-    float2* planes = Xh + (size_t)p.nrows * ZG;       // [ZG * BG][N][KP]
-    const int plane_sz = N * KP;
+    int4* pinfo = reinterpret_cast<int4*>(Xh + (size_t)p.nrows * ZG);    // [npairs]
+    float2* planes = reinterpret_cast<float2*>(pinfo + p.pan.npairs);     // [ZG * BG][N][KP]
+    const int plane_sz = p.PS;
     const long z0 = (long)ctx.bid * ZG;
     const int zc = (int)((p.nbatch - z0) < ZG ? (p.nbatch - z0) : ZG);
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
+    for (int pr = ctx.tid; pr < p.pan.npairs; pr += ctx.nthr) {
+      int m, n;
+      so3_pair_decode(pr, K, m, n);
+      const int am = m < 0 ? -m : m;
+      const int lmin = am > n ? am : n;
+      pinfo[pr] = make_int4((int)(p.pan.off[pr] / N), K - lmin, m < 0 ? m + N : m, n);
+    }
     // symmetrised half spectrum  Xs = (X[l,m,n] + (-1)^(m-n) conj X[l,-m,-n]) / 2
     for (int it = ctx.tid; it < p.nrows * ZG; it += ctx.nthr) {
       const int r = it / ZG, zz = it - r * ZG;
@@ -117,18 +118,13 @@ struct so3_inv_fused_impl {
       // ---- Wigner contraction over l: one (pair, beta) per work item, ZG accumulators -------
       for (int it = ctx.tid; it < p.pan.npairs * bc; it += ctx.nthr) {
         const int pr = it / bc, bi = it - pr * bc;
-        int m, n;
-        so3_pair_decode(pr, K, m, n);
-        const int am = m < 0 ? -m : m;
-        const int lmin = am > n ? am : n;
-        const int L = K - lmin;
-        const long off = p.pan.off[pr];
-        const float* w = p.pan.data + off + bg0 + bi;
-        const float2* xs = Xh + (off / N) * ZG;
+        const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
+        const float* w = p.pan.data + (long)info.x * N + bg0 + bi;
+        const float2* xs = Xh + info.x * ZG;
         float2 acc[ZG];
 #pragma unroll
         for (int z = 0; z < ZG; ++z) acc[z] = make_float2(0.f, 0.f);
-        for (int li = 0; li < L; ++li) {
+        for (int li = 0; li < info.y; ++li) {
           const float wv = w[li * N];
 #pragma unroll
           for (int z = 0; z < ZG; ++z) {
@@ -137,12 +133,13 @@ struct so3_inv_fused_impl {
             acc[z].y = fmaf(wv, xv.y, acc[z].y);
           }
         }
-        const int row = m < 0 ? m + N : m;
+        float2* pl = planes + (size_t)bi * plane_sz + info.z * KP + info.w;
+        const bool mirror = (info.w == 0 && info.z > 0);  // n = 0, m > 0: row N - m holds the conjugate
 #pragma unroll
         for (int z = 0; z < ZG; ++z) {
-          float2* pl = planes + (size_t)(z * p.BG + bi) * plane_sz;
-          pl[row * KP + n] = acc[z];
-          if (n == 0 && m > 0) pl[(N - m) * KP] = make_float2(acc[z].x, -acc[z].y);
+          pl[(size_t)z * p.BG * plane_sz] = acc[z];
+          if (mirror)
+            pl[(size_t)z * p.BG * plane_sz + (N - 2 * info.z) * KP] = make_float2(acc[z].x, -acc[z].y);
         }
       }
       ctx.sync();
@@ -167,8 +164,10 @@ struct so3_inv_fused_impl {
       for (int it = ctx.tid; it < ZG * bc * (N / 2); it += ctx.nthr) {
         const int ap = it % (N / 2), zb = it / (N / 2);
         const int bi = zb % bc, z = zb / bc;
-        float2* r1 = planes + (size_t)(z * p.BG + bi) * plane_sz + (2 * ap) * KP;
-        float2* r2 = r1 + KP;
+        // rows alpha = ap and ap + N/2 share one complex transform (row stride KP is odd, so
+        // consecutive threads hit distinct banks)
+        float2* r1 = planes + (size_t)(z * p.BG + bi) * plane_sz + ap * KP;
+        float2* r2 = r1 + (N / 2) * KP;
         float2 v[N];
         {
           const float2 t1 = r1[0], t2 = r2[0];
@@ -189,42 +188,34 @@ struct so3_inv_fused_impl {
         fft_reg<N, +1>(v, tw);
         float add = 0.f;
         if (p.bias) add = p.bias[(z0 + z) % p.nfeat];
-        float* o1 = reinterpret_cast<float*>(r1);
-        float* o2 = reinterpret_cast<float*>(r2);
-        static_for<0, N>([&](auto ic) {
-          constexpr int g = decltype(ic)::value;
-          constexpr int pg = fft_reg_pos<N>(g);
-          const float2 t = v[pg];
-          o1[g] = t.x + add;
-          o2[g] = t.y + add;
-        });
-      }
-      ctx.sync();
-      // ---- store whole planes ----------------------------------------------------------------
-      if (p.out_stride == 1) {
-        for (int it = ctx.tid; it < zc * bc * N * (N / 2); it += ctx.nthr) {
-          const int g2 = it % (N / 2);
-          int t = it / (N / 2);
-          const int a = t % N;
-          t /= N;
-          const int bi = t % bc, z = t / bc;
-          const float* src = reinterpret_cast<const float*>(
-              planes + (size_t)(z * p.BG + bi) * plane_sz + a * KP);
-          const float2 val = make_float2(src[2 * g2], src[2 * g2 + 1]);
-          float* dst = p.out + (((z0 + z) * N + bg0 + bi) * N + a) * (long)N + 2 * g2;
-          *reinterpret_cast<float2*>(dst) = val;
-        }
-      } else {
-        for (int it = ctx.tid; it < zc * bc * N * N; it += ctx.nthr) {
-          const int g = it % N;
-          int t = it / N;
-          const int a = t % N;
-          t /= N;
-          const int bi = t % bc, z = t / bc;
-          const float* src = reinterpret_cast<const float*>(
-              planes + (size_t)(z * p.BG + bi) * plane_sz + a * KP);
-          const long e = (((z0 + z) * N + bg0 + bi) * N + a) * (long)N + g;
-          p.out[e * p.out_stride + p.out_off] = src[g];
+        // store the two finished rows straight from registers (the plane is contiguous in memory)
+        if (z < zc) {
+          const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;   // first float of row ap
+          const long row2 = row1 + (long)(N / 2) * N;
+          if (p.out_stride == 1) {
+            constexpr int V = (N % 4 == 0) ? 4 : 2;
+            static_for<0, N / V>([&](auto ic) {
+              constexpr int g = V * decltype(ic)::value;
+              constexpr int p0 = fft_reg_pos<N>(g), p1 = fft_reg_pos<N>(g + 1);
+              if constexpr (V == 4) {
+                constexpr int p2 = fft_reg_pos<N>(g + 2), p3 = fft_reg_pos<N>(g + 3);
+                *reinterpret_cast<float4*>(p.out + row1 + g) =
+                    make_float4(v[p0].x + add, v[p1].x + add, v[p2].x + add, v[p3].x + add);
+                *reinterpret_cast<float4*>(p.out + row2 + g) =
+                    make_float4(v[p0].y + add, v[p1].y + add, v[p2].y + add, v[p3].y + add);
+              } else {
+                *reinterpret_cast<float2*>(p.out + row1 + g) = make_float2(v[p0].x + add, v[p1].x + add);
+                *reinterpret_cast<float2*>(p.out + row2 + g) = make_float2(v[p0].y + add, v[p1].y + add);
+              }
+            });
+          } else {
+            static_for<0, N>([&](auto ic) {
+              constexpr int g = decltype(ic)::value;
+              constexpr int pg = fft_reg_pos<N>(g);
+              p.out[(row1 + g) * p.out_stride + p.out_off] = v[pg].x + add;
+              p.out[(row2 + g) * p.out_stride + p.out_off] = v[pg].y + add;
+            });
+          }
         }
       }
       ctx.sync();
@@ -240,7 +231,7 @@ struct FwdFusedParams {
   long out_zstride;
   PanelsDev pan;       // beta grid of b_in, nl = b_out, K
   const float2* tw;
-  int nbatch, K, BG, KP, nrows, mode, relu;
+  int nbatch, K, BG, KP, PS, nrows, mode, relu;
 };
 
 template <int N>
@@ -251,7 +242,7 @@ struct so3_fwd_fused_impl {
     float2* tw = reinterpret_cast<float2*>(smem);
     float2* acc = tw + N;                               // [nrows][ZG]
     float2* planes = acc + (size_t)p.nrows * ZG;        // [ZG * BG][N][KP]
-    const int plane_sz = N * KP;
+    const int plane_sz = p.PS;
     const long z0 = (long)ctx.bid * ZG;
     const int zc = (int)((p.nbatch - z0) < ZG ? (p.nbatch - z0) : ZG);
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
@@ -260,55 +251,53 @@ struct so3_fwd_fused_impl {
 
     for (int bg0 = 0; bg0 < N; bg0 += p.BG) {
       const int bc = (N - bg0) < p.BG ? (N - bg0) : p.BG;
-      // ---- load planes (rows of N floats at a stride of 2 KP floats) -------------------------
-      if (p.in_stride == 1) {
-        for (int it = ctx.tid; it < ZG * bc * N * (N / 2); it += ctx.nthr) {
-          const int g2 = it % (N / 2);
-          int t = it / (N / 2);
-          const int a = t % N;
-          t /= N;
-          const int bi = t % bc, z = t / bc;
-          float2 val = make_float2(0.f, 0.f);
-          if (z < zc) {
-            const float* src = p.x + (((z0 + z) * N + bg0 + bi) * N + a) * (long)N + 2 * g2;
-            val = *reinterpret_cast<const float2*>(src);
-            if (p.relu) {
-              val.x = val.x > 0.f ? val.x : 0.f;
-              val.y = val.y > 0.f ? val.y : 0.f;
-            }
-          }
-          float* dst = reinterpret_cast<float*>(planes + (size_t)(z * p.BG + bi) * plane_sz + a * KP);
-          dst[2 * g2] = val.x;
-          dst[2 * g2 + 1] = val.y;
-        }
-      } else {
-        for (int it = ctx.tid; it < ZG * bc * N * N; it += ctx.nthr) {
-          const int g = it % N;
-          int t = it / N;
-          const int a = t % N;
-          t /= N;
-          const int bi = t % bc, z = t / bc;
-          float val = 0.f;
-          if (z < zc) {
-            const long e = (((z0 + z) * N + bg0 + bi) * N + a) * (long)N + g;
-            val = p.x[e * p.in_stride + p.in_off];
-            if (p.relu) val = val > 0.f ? val : 0.f;
-          }
-          reinterpret_cast<float*>(planes + (size_t)(z * p.BG + bi) * plane_sz + a * KP)[g] = val;
-        }
-      }
-      ctx.sync();
-      // ---- row FFTs gamma -> n, two real rows per complex transform --------------------------
+      // ---- row FFTs gamma -> n: each thread reads two real rows (alpha, alpha + N/2) straight
+      //      from global memory into registers (optional ReLU), transforms them as one complex
+      //      sequence and leaves the n < K half spectra of both rows in shared memory -----------
       for (int it = ctx.tid; it < ZG * bc * (N / 2); it += ctx.nthr) {
         const int ap = it % (N / 2), zb = it / (N / 2);
         const int bi = zb % bc, z = zb / bc;
-        float2* r1 = planes + (size_t)(z * p.BG + bi) * plane_sz + (2 * ap) * KP;
-        float2* r2 = r1 + KP;
-        const float* f1 = reinterpret_cast<const float*>(r1);
-        const float* f2 = reinterpret_cast<const float*>(r2);
+        float2* r1 = planes + (size_t)(z * p.BG + bi) * plane_sz + ap * KP;
+        float2* r2 = r1 + (N / 2) * KP;
         float2 v[N];
+        if (z < zc) {
+          const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;
+          const long row2 = row1 + (long)(N / 2) * N;
+          if (p.in_stride == 1) {
+            constexpr int V = (N % 4 == 0) ? 4 : 2;
+            static_for<0, N / V>([&](auto ic) {
+              constexpr int g = V * decltype(ic)::value;
+              if constexpr (V == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(p.x + row1 + g);
+                const float4 b = *reinterpret_cast<const float4*>(p.x + row2 + g);
+                v[g] = make_float2(a.x, b.x);
+                v[g + 1] = make_float2(a.y, b.y);
+                v[g + 2] = make_float2(a.z, b.z);
+                v[g + 3] = make_float2(a.w, b.w);
+              } else {
+                const float2 a = *reinterpret_cast<const float2*>(p.x + row1 + g);
+                const float2 b = *reinterpret_cast<const float2*>(p.x + row2 + g);
+                v[g] = make_float2(a.x, b.x);
+                v[g + 1] = make_float2(a.y, b.y);
+              }
+            });
+          } else {
 #pragma unroll
-        for (int g = 0; g < N; ++g) v[g] = make_float2(f1[g], f2[g]);
+            for (int g = 0; g < N; ++g)
+              v[g] = make_float2(p.x[(row1 + g) * p.in_stride + p.in_off],
+                                 p.x[(row2 + g) * p.in_stride + p.in_off]);
+          }
+          if (p.relu) {
+#pragma unroll
+            for (int g = 0; g < N; ++g) {
+              v[g].x = v[g].x > 0.f ? v[g].x : 0.f;
+              v[g].y = v[g].y > 0.f ? v[g].y : 0.f;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < N; ++g) v[g] = make_float2(0.f, 0.f);
+        }
         fft_reg<N, -1>(v, tw);
         static_for<0, N / 2>([&](auto ic) {
           constexpr int n = decltype(ic)::value;
@@ -338,22 +327,27 @@ struct so3_fwd_fused_impl {
         });
       }
       ctx.sync();
-      // ---- accumulate the Wigner contraction over the betas of this group ---------------------
-      for (int it = ctx.tid; it < p.nrows * ZG; it += ctx.nthr) {
-        const int r = it / ZG, z = it - r * ZG;
+      // ---- accumulate the Wigner contraction over the betas of this group: one panel row
+      //      (l, m, n) per thread, all ZG batch elements -----------------------------------------
+      for (int r = ctx.tid; r < p.nrows; r += ctx.nthr) {
         int l, m, n;
         rowmap_unpack(p.pan.rowmap[r], l, m, n);
         const float* w = p.pan.data + (long)r * N + bg0;
-        const float2* src = planes + (size_t)(z * p.BG) * plane_sz + (m < 0 ? m + N : m) * KP + n;
-        float ar = 0.f, ai = 0.f;
+        const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
+        float2 a[ZG];
+#pragma unroll
+        for (int z = 0; z < ZG; ++z) a[z] = acc[r * ZG + z];
         for (int bi = 0; bi < bc; ++bi) {
           const float wv = w[bi];
-          const float2 xv = src[(size_t)bi * plane_sz];
-          ar = fmaf(wv, xv.x, ar);
-          ai = fmaf(wv, xv.y, ai);
+#pragma unroll
+          for (int z = 0; z < ZG; ++z) {
+            const float2 xv = src[(size_t)(z * p.BG + bi) * plane_sz];
+            a[z].x = fmaf(wv, xv.x, a[z].x);
+            a[z].y = fmaf(wv, xv.y, a[z].y);
+          }
         }
-        float2 c = acc[it];
-        acc[it] = make_float2(c.x + ar, c.y + ai);
+#pragma unroll
+        for (int z = 0; z < ZG; ++z) acc[r * ZG + z] = a[z];
       }
       ctx.sync();
     }
@@ -427,17 +421,29 @@ __global__ void __launch_bounds__(256) so3_fwd_fused(const FwdFusedParams p) {
 
 constexpr int kFusedMaxN = 32;
 
-inline int fused_kp(int N) { return N / 2 + 1; }
+// Row stride of a plane in complex numbers: >= N/2 (a row must hold N floats) and odd, so that
+// threads walking down a column of rows fall into distinct shared-memory banks.
+inline int fused_kp(int N) { return (N / 2) % 2 == 0 ? N / 2 + 1 : N / 2 + 2; }
+// Plane stride in complex numbers: padded so that plane p+1 starts K 8-byte banks after plane p
+// (threads of consecutive planes reading the same row then continue the bank sequence).
+inline int fused_plane_stride(int N, int K) {
+  int ps = N * fused_kp(N);
+  while (ps % 16 != K % 16) ++ps;
+  return ps;
+}
+// Betas per group: the largest divisor of N that keeps the per-group transform count
+// (ZG * BG * N/2 threads, one transform each) within one pass of a 256-thread block.
 inline int fused_bg(int N) {
-  const int per_beta = kFusedZG * N * fused_kp(N) * (int)sizeof(float2);
-  int bg = (32 * 1024) / per_beta;
-  if (bg < 1) bg = 1;
-  if (bg > N) bg = N;
-  return bg;
+  int best = 1;
+  for (int d = 1; d <= N; ++d)
+    if (N % d == 0 && d <= kMaxBG && kFusedZG * d * (N / 2) <= 256) best = d;
+  return best;
 }
 inline size_t fused_smem_bytes(int N, int nrows) {
+  const int K = N / 2;  // upper bound of the pair count: so3_npairs(K)
   return (size_t)N * sizeof(float2) + (size_t)nrows * kFusedZG * sizeof(float2) +
-         (size_t)kFusedZG * fused_bg(N) * N * fused_kp(N) * sizeof(float2);
+         (size_t)so3_npairs(K) * sizeof(int4) +
+         (size_t)kFusedZG * fused_bg(N) * (N * fused_kp(N) + 16) * sizeof(float2);
 }
 
 }  // namespace s2c
