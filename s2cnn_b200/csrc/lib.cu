@@ -640,7 +640,8 @@ int s2c_so3_integrate(const float* x, float* out, long n, int b, int relu, void*
   IntegrateParams p;
   p.x = x; p.out = out; p.n = n; p.N = 2 * b; p.relu = relu;
   S2C_TRY(TableCache::get().quad_weights(b, &p.w));
-  return S2C_LAUNCH(so3_integrate_fwd, n, 256, 256 * sizeof(float), as_stream(st), p);
+  return S2C_LAUNCH(so3_integrate_fwd, (n + kIntegrateWarps - 1) / kIntegrateWarps,
+                    32 * kIntegrateWarps, 32 * kIntegrateWarps * sizeof(float), as_stream(st), p);
 }
 
 int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n, int b, int relu,

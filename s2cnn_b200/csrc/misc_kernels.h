@@ -122,26 +122,37 @@ struct IntegrateParams {
   int relu;          // apply max(x, 0) before summing (fused activation, optional)
 };
 
+constexpr int kIntegrateWarps = 8;  // signals per block (one warp each)
+
 S2C_KERNEL(so3_integrate_fwd, IntegrateParams) {
-  // one block per signal; fixed-order tree reduction (deterministic)
-  float* red = reinterpret_cast<float*>(smem);
-  const long z = ctx.bid;
-  const int plane = p.N * p.N;
-  const long total = (long)p.N * plane;
-  const float* src = p.x + z * total;
+  // one warp per signal: 16-byte loads (a group of 4 samples never straddles a beta plane because
+  // (2b)^2 is a multiple of 4), lane partials through shared memory, fixed summation order
+  float* red = reinterpret_cast<float*>(smem);  // [kIntegrateWarps][32]
+  const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
+  const long z = (long)ctx.bid * kIntegrateWarps + warp;
+  const int plane4 = p.N * p.N / 4;
+  const int total4 = p.N * plane4;
   float acc = 0.f;
-  for (long e = ctx.tid; e < total; e += ctx.nthr) {
-    float v = src[e];
-    if (p.relu) v = v > 0.f ? v : 0.f;
-    acc = fmaf(p.w[e / plane], v, acc);
+  if (z < p.n) {
+    const float4* src = reinterpret_cast<const float4*>(p.x + z * (long)total4 * 4);
+    for (int e = lane; e < total4; e += 32) {
+      float4 v = src[e];
+      if (p.relu) {
+        v.x = v.x > 0.f ? v.x : 0.f;
+        v.y = v.y > 0.f ? v.y : 0.f;
+        v.z = v.z > 0.f ? v.z : 0.f;
+        v.w = v.w > 0.f ? v.w : 0.f;
+      }
+      acc = fmaf(p.w[e / plane4], (v.x + v.y) + (v.z + v.w), acc);
+    }
   }
   red[ctx.tid] = acc;
   ctx.sync();
-  for (int s = ctx.nthr >> 1; s > 0; s >>= 1) {
-    if (ctx.tid < s) red[ctx.tid] += red[ctx.tid + s];
-    ctx.sync();
+  if (lane == 0 && z < p.n) {
+    float s = 0.f;
+    for (int i = 0; i < 32; ++i) s += red[warp * 32 + i];
+    p.out[z] = s;
   }
-  if (ctx.tid == 0) p.out[z] = red[0];
 }
 
 struct IntegrateBwdParams {
