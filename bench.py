@@ -209,8 +209,12 @@ def dist_setup(n_gpus):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
-        backend = "nccl" if torch.cuda.is_available() else "gloo"
-        dist.init_process_group(backend, rank=rank, world_size=world)
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", rank=rank, world_size=world,
+                                    device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
     return world, rank, local
 
 
@@ -259,6 +263,9 @@ def cpu_baseline(batch, repeats=3):
 
 def run_reference(args):
     world, rank, _ = dist_setup(args.gpus)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
