@@ -12,6 +12,7 @@
 #include "fft_device.h"
 #include "so3_kernels.h"
 #include "so3_fused_kernels.h"
+#include "wigner_tiled.h"
 #include "cgemm_kernels.h"
 #include "so3_mm_tc.h"
 #include "misc_kernels.h"
@@ -106,6 +107,13 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     w.ZT = (int)std::min<long>(32, zc);
     w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
     w.mode = mode;
+    if (N % 4 == 0 && fwd_wigner_t_smem(N, b_out) <= (size_t)dev_smem_limit() - 1024) {
+      w.ZT = kWigZT;
+      w.nzt = (int)((zc + kWigZT - 1) / kWigZT);
+      S2C_TRY(S2C_LAUNCH(so3_fwd_wigner_t, (long)pan.npairs * w.nzt, kThreads,
+                         fwd_wigner_t_smem(N, b_out), st, w));
+      continue;
+    }
     const size_t wsm = align_up((size_t)b_out * (N + 1) * sizeof(float), 16) +
                        (size_t)w.ZT * (N + 1) * sizeof(float2);
     S2C_TRY(S2C_LAUNCH(so3_fwd_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
@@ -179,8 +187,15 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     w.ZT = (int)std::min<long>(32, zc);
     w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
     w.mode = mode;
-    const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
-    S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+    if (N % 4 == 0 && inv_wigner_t_smem(N, K) <= (size_t)dev_smem_limit() - 1024) {
+      w.ZT = kWigZT;
+      w.nzt = (int)((zc + kWigZT - 1) / kWigZT);
+      S2C_TRY(S2C_LAUNCH(so3_inv_wigner_t, (long)pan.npairs * w.nzt, kThreads,
+                         inv_wigner_t_smem(N, K), st, w));
+    } else {
+      const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
+      S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+    }
     InvAlphaParams a;
     a.s = s;
     a.out = (float*)t;

@@ -277,3 +277,22 @@ def test_s2_product_synthesis_fused(backend, b, nb, fi, fo):
         assert_close(ops.s2_conv_synthesis(xs.to(dev), ys.to(dev), bias.to(dev)), ref, "general")
     finally:
         ops.lib.s2c_debug_force_general_path(0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(8, 8, 37), (6, 4, 67), (4, 6, 3)])
+def test_general_path_tiled_wigner_odd_batches(backend, b_in, b_out, nbatch):
+    """The register-tiled Wigner kernels of the general path with batch counts that leave partial
+    (and odd) tiles."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in * 31 + nbatch)
+    x = torch.randn(nbatch, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen)
+    s = torch.randn(n3(b_in), nbatch, 2, generator=gen)
+    ops.lib.s2c_debug_force_general_path(1)
+    try:
+        assert_close(ops.so3_rfft(x.to(dev), False, b_out), O.so3_rfft(x, False, b_out), "rfft")
+        assert_close(ops.so3_rifft(s.to(dev), False, b_out), O.so3_rifft(s, False, b_out), "rifft")
+        assert_close(ops.so3_fft(torch.stack((x, -x), -1).to(dev), False, b_out),
+                     O.so3_fft(torch.stack((x, -x), -1), False, b_out), "fft")
+    finally:
+        ops.lib.s2c_debug_force_general_path(0)
