@@ -98,30 +98,26 @@ def oracle_params(seed=0):
 # algorithmic bytes per launch of each kernel of the net forward at batch B (what the kernel must
 # read and write once: its own inputs and outputs, constant tables excluded)
 def kernel_bytes(B):
+    """Per forward pass, per kernel name: bytes the kernel has to move once - its own inputs and
+    outputs, constant tables excluded - summed over its launches in the step."""
     b0, b1, b2, f0, f1, f2 = (NET[k] for k in ("b0", "b1", "b2", "f0", "f1", "f2"))
     c = 8  # bytes per complex
+    sig1 = B * f1 * (2 * b1) ** 3 * 4   # conv1 output / conv2 input signal
+    sig2 = B * f2 * (2 * b2) ** 3 * 4   # conv2 output signal
     out = {}
-    # conv1 synthesis at b1 (K = b1), nbatch = B*f1
-    z = B * f1
-    N, K = 2 * b1, b1
-    out["so3_inv_wigner@conv1"] = n3(b1) * z * c + K * (2 * K - 1) * z * N * c
-    out["so3_inv_alpha@conv1"] = K * (2 * K - 1) * z * N * c + z * K * N * N * c
-    out["so3_inv_gamma@conv1"] = z * K * N * N * c + z * N ** 3 * 4
-    # conv2 analysis b1 -> b2 (K = b2), nbatch = B*f1
-    N, K = 2 * b1, b2
-    out["so3_fwd_gamma@conv2"] = z * N ** 3 * 4 + z * K * N * N * c
-    out["so3_fwd_alpha@conv2"] = z * K * N * N * c + K * (2 * K - 1) * z * N * c
-    out["so3_fwd_wigner@conv2"] = K * (2 * K - 1) * z * N * c + n3(b2) * z * c
-    # conv2 synthesis at b2, nbatch = B*f2
-    z2 = B * f2
-    N, K = 2 * b2, b2
-    out["so3_inv_wigner@conv2"] = n3(b2) * z2 * c + K * (2 * K - 1) * z2 * N * c
-    out["so3_inv_alpha@conv2"] = K * (2 * K - 1) * z2 * N * c + z2 * K * N * N * c
-    out["so3_inv_gamma@conv2"] = z2 * K * N * N * c + z2 * N ** 3 * 4
-    out["so3_integrate_fwd"] = z2 * (2 * b2) ** 3 * 4 + z2 * 4
-    # spectral products (tensor-bound in principle; bytes listed for completeness)
-    out["cgemm_grouped@s2_mm"] = b1 * b1 * (B * f0 + f0 * f1) * c + n3(b1) * B * f1 * c
-    out["cgemm_grouped@so3_mm"] = n3(b2) * (B * f1 + f1 * f2 + B * f2) * c
+    # S2 analysis of the input (two small passes of the general kernels, n = 0 only)
+    N0, K0 = 2 * b0, b1
+    out["so3_fwd_alpha"] = B * f0 * N0 * N0 * 4 + (2 * K0 - 1) * B * f0 * N0 * c
+    out["so3_fwd_wigner"] = (2 * K0 - 1) * B * f0 * N0 * c + b1 * b1 * B * f0 * c
+    # kernel-grid -> spectrum transforms of both layers
+    out["rft_forward"] = (f0 * f1 * 24 * 4 + b1 * b1 * f0 * f1 * c) + (f1 * f2 * 192 * 4 + n3(b2) * f1 * f2 * c)
+    # conv1: s2_mm fused into the synthesis (reads the two S2 spectra, writes the signal)
+    # conv2 synthesis: reads the SO(3) spectrum, writes the signal
+    out["so3_inv_fused"] = (b1 * b1 * (B * f0 + f0 * f1) * c + sig1) + (n3(b2) * B * f2 * c + sig2)
+    # conv2 analysis (ReLU on load): reads the signal, writes the spectrum
+    out["so3_fwd_fused"] = sig1 + n3(b2) * B * f1 * c
+    out["so3_mm_tc_kernel"] = n3(b2) * (B * f1 + f1 * f2 + B * f2) * c
+    out["so3_integrate_fwd"] = sig2 + B * f2 * 4
     return out
 
 
@@ -432,23 +428,20 @@ def run_ours(args):
     kb = kernel_bytes(B)
     kernels = []
     for name, (cnt, ms) in per_kernel.items():
-        inst = {k: v for k, v in kb.items() if k.split("@")[0] == name}
-        per_step_bytes = sum(inst.values())
-        launches_per_step = cnt / args.steps
-        avg_ms = ms / cnt
-        kernels.append({"kernel": name, "launches_per_step": launches_per_step,
-                        "ms_per_step": ms / args.steps, "avg_launch_ms": avg_ms,
+        per_step_bytes = kb.get(name, 0)
+        kernels.append({"kernel": name, "launches_per_step": cnt / args.steps,
+                        "ms_per_step": ms / args.steps, "avg_launch_ms": ms / cnt,
                         "alg_bytes_per_step": per_step_bytes,
                         "GBps": per_step_bytes / (ms / args.steps * 1e-3) / 1e9 if ms > 0 else None})
     kernels.sort(key=lambda k: -k["ms_per_step"])
     top = kernels[0]
     flops = net_flops(B)
-    if top["kernel"] == "cgemm_grouped":
+    if top["kernel"] == "so3_mm_tc_kernel":
         # dominant kernel is the spectral product: tensor roofline, TF32 dense = 1/2 bf16
-        fl = flops["so3_mm"] + flops["s2_mm"]
+        fl = flops["so3_mm"]
         ach = fl / (top["ms_per_step"] * 1e-3) / 1e12
         peak = bf16_tf / 2
-        roofline = {"kernel": "cgemm_grouped (s2_mm + so3_mm)", "bound": "tensor", "achieved": ach,
+        roofline = {"kernel": "so3_mm_tc_kernel", "bound": "tensor", "achieved": ach,
                     "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
                     "peak_source": peak_kind + " bf16 / 2 (TF32 dense)"}
     else:

@@ -22,6 +22,7 @@
 
 #include "backend.h"
 #include "fft_device.h"
+#include "fft_twostep.h"
 #include "tables.h"
 
 namespace s2c {
@@ -35,22 +36,36 @@ struct FftSmem {
   float2* tw;
   unsigned short* pos;
   float2* data;
+  float2* tmp;   // second buffer of the two-step FFT (lengths 64 / 128 / 256), else unused
 };
-S2C_D FftSmem fft_smem_carve(unsigned char* smem, int n) {
+S2C_HD size_t fft_smem_head_bytes(int n) { return align_up((size_t)n * (sizeof(float2) + 2), 16); }
+S2C_D FftSmem fft_smem_carve(unsigned char* smem, int n, int rows) {
   FftSmem s;
   s.tw = reinterpret_cast<float2*>(smem);
   s.pos = reinterpret_cast<unsigned short*>(smem + (size_t)n * sizeof(float2));
-  s.data = reinterpret_cast<float2*>(smem + align_up((size_t)n * (sizeof(float2) + 2), 16));
+  s.data = reinterpret_cast<float2*>(smem + fft_smem_head_bytes(n));
+  s.tmp = s.data + (size_t)rows * (n + 1);
   return s;
 }
 inline size_t fft_smem_bytes(int n, int rows) {
-  return align_up((size_t)n * (sizeof(float2) + 2), 16) + (size_t)rows * (n + 1) * sizeof(float2);
+  size_t b = fft_smem_head_bytes(n) + (size_t)rows * (n + 1) * sizeof(float2);
+  if (fft_twostep_supported(n)) b += (size_t)rows * fft_twostep_ld2(n) * sizeof(float2);
+  return b;
 }
+// Twiddles and the frequency -> position map.  The two-step FFT leaves its output in natural
+// order, so its map is the identity.
 S2C_D void fft_smem_load_tables(const Ctx& ctx, const FftSmem& s, const FftDev& f) {
+  const bool natural = fft_twostep_supported(f.desc.n);
   for (int i = ctx.tid; i < f.desc.n; i += ctx.nthr) {
     s.tw[i] = f.tw[i];
-    s.pos[i] = f.pos[i];
+    s.pos[i] = natural ? (unsigned short)i : f.pos[i];
   }
+}
+// In-place FFT of `cnt` rows (stride ld) held in s.data; ends with a block barrier.
+template <int DIR>
+S2C_D void fft_rows(const Ctx& ctx, const FftSmem& s, const FftDesc& d, int cnt, int ld) {
+  if (fft_twostep_supported(d.n)) fft_twostep<DIR>(ctx, s.data, s.tmp, d.n, cnt, ld, s.tw);
+  else fft_dif_inplace<DIR>(ctx, s.data, d, cnt, ld, 1, false, s.tw);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -67,7 +82,7 @@ struct FwdGammaParams {
 
 S2C_KERNEL(so3_fwd_gamma, FwdGammaParams) {
   const int N = p.N, ld = N + 1;
-  FftSmem s = fft_smem_carve(smem, N);
+  FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
   const long pair0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
@@ -79,7 +94,7 @@ S2C_KERNEL(so3_fwd_gamma, FwdGammaParams) {
     s.data[g * ld + gam] = make_float2(a, b);
   }
   ctx.sync();
-  fft_dif_inplace<-1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  fft_rows<-1>(ctx, s, p.fft.desc, cnt, ld);
   // separate the two real rows packed in one complex transform; keep n < K
   for (int it = ctx.tid; it < cnt * p.K; it += ctx.nthr) {
     const int n = it / cnt, g = it - n * cnt;
@@ -114,7 +129,7 @@ struct FwdAlphaParams {
 
 S2C_KERNEL(so3_fwd_alpha, FwdAlphaParams) {
   const int N = p.N, ld = N + 1;
-  FftSmem s = fft_smem_carve(smem, N);
+  FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
   const long row0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
@@ -131,7 +146,7 @@ S2C_KERNEL(so3_fwd_alpha, FwdAlphaParams) {
     }
   }
   ctx.sync();
-  fft_dif_inplace<-1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  fft_rows<-1>(ctx, s, p.fft.desc, cnt, ld);
   const int nm = 2 * p.K - 1;
   for (int it = ctx.tid; it < cnt * nm; it += ctx.nthr) {
     const int mi = it / cnt, g = it - mi * cnt;
@@ -298,7 +313,7 @@ struct InvAlphaParams {
 
 S2C_KERNEL(so3_inv_alpha, InvAlphaParams) {
   const int N = p.N, ld = N + 1;
-  FftSmem s = fft_smem_carve(smem, N);
+  FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
   const long row0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
@@ -319,7 +334,7 @@ S2C_KERNEL(so3_inv_alpha, InvAlphaParams) {
     if (p.herm_n0 && n == 0 && m > 0) s.data[g * ld + N - m] = make_float2(v.x, -v.y);
   }
   ctx.sync();
-  fft_dif_inplace<+1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  fft_rows<+1>(ctx, s, p.fft.desc, cnt, ld);
   if (p.out_real) {
     for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
       const int g = it / N, a = it - g * N;
@@ -351,7 +366,7 @@ struct InvGammaParams {
 
 S2C_KERNEL(so3_inv_gamma, InvGammaParams) {
   const int N = p.N, ld = N + 1;
-  FftSmem s = fft_smem_carve(smem, N);
+  FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
   const long pair0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
@@ -375,7 +390,7 @@ S2C_KERNEL(so3_inv_gamma, InvGammaParams) {
     }
   }
   ctx.sync();
-  fft_dif_inplace<+1>(ctx, s.data, p.fft.desc, cnt, ld, 1, false, s.tw);
+  fft_rows<+1>(ctx, s, p.fft.desc, cnt, ld);
   for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
     const int g = it / N, gam = it - g * N;
     const long pid = pair0 + g;

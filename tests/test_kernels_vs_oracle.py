@@ -296,3 +296,15 @@ def test_general_path_tiled_wigner_odd_batches(backend, b_in, b_out, nbatch):
                      O.so3_fft(torch.stack((x, -x), -1), False, b_out), "fft")
     finally:
         ops.lib.s2c_debug_force_general_path(0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(32, 32, 1), (32, 9, 2), (10, 32, 2)])
+def test_bandwidth_32_two_step_fft(backend, b_in, b_out, nbatch):
+    """2b = 64 takes the two-step register FFT (8 x 8) inside the general path."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in + b_out)
+    x = torch.randn(nbatch, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen)
+    s = torch.randn(n3(b_in), nbatch, 2, generator=gen)
+    assert_close(ops.so3_rfft(x.to(dev), False, b_out), O.so3_rfft(x, False, b_out), "rfft")
+    assert_close(ops.so3_rifft(s.to(dev), False, b_out), O.so3_rifft(s, False, b_out), "rifft")
