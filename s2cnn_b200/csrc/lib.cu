@@ -29,7 +29,15 @@ static bool g_force_general = false;  // test switch: route small bandwidths thr
 
 static inline stream_t as_stream(void* s) { return (stream_t)s; }
 
-static inline int fft_group(int N) { return std::max(1, std::min(256, 4096 / N)); }
+// Rows (or row pairs) per block of the FFT passes: about 4096 complex numbers of shared memory,
+// and a divisor of `period` so that a block never straddles two planes / two (z, n) slabs.
+static inline int fft_group(int N, int period) {
+  const int cap = std::max(1, std::min(256, 4096 / N));
+  int g = 1;
+  for (int d = 1; d <= period && d <= cap; ++d)
+    if (period % d == 0) g = d;
+  return g;
+}
 
 static size_t so3_ws_per_z(int N, int K) {
   // two scratch arrays of complex numbers: [z][K][N][N] and [K][2K-1][z][N]
@@ -75,7 +83,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
   if (chunk < 1 || ws == nullptr)
     return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" +
                                        std::to_string(per_z) + " bytes needed)");
-  const int G = fft_group(N);
+  const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
@@ -86,10 +94,10 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     g.in_stride = in_stride;
     g.in_off = in_off;
     g.u = u;
-    g.N = N; g.b = b_in; g.K = K; g.G = G;
+    g.N = N; g.b = b_in; g.K = K; g.G = Gg;
     g.npairs = zc * N * b_in;
     g.fft = fft;
-    S2C_TRY(S2C_LAUNCH(so3_fwd_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g));
+    S2C_TRY(S2C_LAUNCH(so3_fwd_gamma, (g.npairs + Gg - 1) / Gg, kThreads, fft_smem_bytes(N, Gg), st, g));
     FwdAlphaParams a;
     a.in = (const float*)u;
     a.in_real = 0;
@@ -172,7 +180,7 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
   if (chunk < 1 || ws == nullptr)
     return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" +
                                        std::to_string(per_z) + " bytes needed)");
-  const int G = fft_group(N);
+  const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
@@ -213,10 +221,10 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     g.bias = bias;
     g.nfeat = nfeat > 0 ? nfeat : 1;
     g.z0 = z0;
-    g.N = N; g.b = b_out; g.K = K; g.G = G;
+    g.N = N; g.b = b_out; g.K = K; g.G = Gg;
     g.npairs = zc * N * b_out;
     g.fft = fft;
-    S2C_TRY(S2C_LAUNCH(so3_inv_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g));
+    S2C_TRY(S2C_LAUNCH(so3_inv_gamma, (g.npairs + Gg - 1) / Gg, kThreads, fft_smem_bytes(N, Gg), st, g));
   }
   return S2C_OK;
 }
@@ -496,7 +504,7 @@ int s2c_s2_fft(const float* x, int x_is_real, float* out, long nbatch, int b_in,
   const size_t per_z = s2_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || !ws) return fail(S2C_ERR_WORKSPACE, "s2c_s2_fft: workspace too small");
-  const int G = fft_group(N);
+  const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     FwdAlphaParams a;
@@ -537,7 +545,7 @@ int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_
   const size_t per_z = s2_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || !ws) return fail(S2C_ERR_WORKSPACE, "s2c_s2_ifft: workspace too small");
-  const int G = fft_group(N);
+  const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     InvWignerParams w;
@@ -814,7 +822,7 @@ int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int 
   S2C_TRY(static_setup(dev));
   S2C_TRY(static_load_tables(dev, b_out, K, for_grad != 0, st));
 
-  const int G = fft_group(N);
+  const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
   float2* t = (float2*)dev.scratch;                   // [z][K][N][N]
   float2* s = t + (size_t)nbatch * K * N * N;         // [K][2K-1][z][N]
@@ -846,10 +854,10 @@ int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int 
   g.bias = bias;
   g.nfeat = nfeature > 0 ? nfeature : 1;
   g.z0 = 0;
-  g.N = N; g.b = b_out; g.K = K; g.G = G;
+  g.N = N; g.b = b_out; g.K = K; g.G = Gg;
   g.npairs = nbatch * N * b_out;
   g.fft = dev.fft;
-  return S2C_LAUNCH(so3_inv_gamma, (g.npairs + G - 1) / G, kThreads, fft_smem, st, g);
+  return S2C_LAUNCH(so3_inv_gamma, (g.npairs + Gg - 1) / Gg, kThreads, fft_smem_bytes(N, Gg), st, g);
 }
 
 }  // extern "C"

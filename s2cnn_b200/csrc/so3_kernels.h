@@ -80,38 +80,70 @@ struct FwdGammaParams {
   FftDev fft;
 };
 
+// G divides b: all row pairs of a block belong to one (z, beta) plane.
 S2C_KERNEL(so3_fwd_gamma, FwdGammaParams) {
   const int N = p.N, ld = N + 1;
   FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
+  const int warp = ctx.tid >> 5, lane = ctx.tid & 31, nwarps = ctx.nthr >> 5;
   const long pair0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
-  for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-    const int g = it / N, gam = it - g * N;
-    const long e = (pair0 + g) * 2 * N + gam;  // rows 2p and 2p+1 are adjacent in memory
-    const float a = p.x[e * p.in_stride + p.in_off];
-    const float b = p.x[(e + N) * p.in_stride + p.in_off];
-    s.data[g * ld + gam] = make_float2(a, b);
+  if (p.in_stride == 1 && N % 4 == 0) {
+    // the block's 2 * cnt rows are one contiguous run: 16-byte loads, four in flight per thread
+    const float4* src = reinterpret_cast<const float4*>(p.x + pair0 * 2 * N);
+    const int n4 = N / 4, total4 = cnt * 2 * n4;
+    float* sdata = reinterpret_cast<float*>(s.data);
+    for (int base = ctx.tid; base < total4; base += 4 * ctx.nthr) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total4) v[u] = src[idx];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total4) {
+          const int row = idx / n4, c4 = idx - row * n4;     // row = 2 g + part
+          float* d = sdata + ((row >> 1) * ld + 4 * c4) * 2 + (row & 1);
+          d[0] = v[u].x;
+          d[2] = v[u].y;
+          d[4] = v[u].z;
+          d[6] = v[u].w;
+        }
+      }
+    }
+  } else {
+    for (int g = warp; g < cnt; g += nwarps) {
+      const long e0 = (pair0 + g) * 2 * N;  // rows 2p and 2p+1 are adjacent in memory
+      for (int gam = lane; gam < N; gam += 32) {
+        const float a = p.x[(e0 + gam) * p.in_stride + p.in_off];
+        const float b = p.x[(e0 + N + gam) * p.in_stride + p.in_off];
+        s.data[g * ld + gam] = make_float2(a, b);
+      }
+    }
   }
   ctx.sync();
   fft_rows<-1>(ctx, s, p.fft.desc, cnt, ld);
   // separate the two real rows packed in one complex transform; keep n < K
-  for (int it = ctx.tid; it < cnt * p.K; it += ctx.nthr) {
-    const int n = it / cnt, g = it - n * cnt;
-    const long pid = pair0 + g;
-    const int pp = (int)(pid % p.b);
-    const long zb = pid / p.b;
-    const int beta = (int)(zb % N);
-    const long z = zb / N;
-    const float2 zk = s.data[g * ld + s.pos[n]];
-    const float2 zc = s.data[g * ld + s.pos[n == 0 ? 0 : N - n]];
-    float4 o;
-    o.x = 0.5f * (zk.x + zc.x);
-    o.y = 0.5f * (zk.y - zc.y);
-    o.z = 0.5f * (zk.y + zc.y);
-    o.w = -0.5f * (zk.x - zc.x);
-    const long idx = ((z * p.K + n) * N + beta) * N + 2 * pp;
-    *reinterpret_cast<float4*>(p.u + idx) = o;
+  const long zb = pair0 / p.b;
+  const int pp0 = (int)(pair0 - zb * p.b);
+  const int beta = (int)(zb % N);
+  const long z = zb / N;
+  float2* ubase = p.u + ((z * p.K) * N + beta) * (long)N + 2 * pp0;
+  for (int n = warp; n < p.K; n += nwarps) {
+    const int pk = s.pos[n], pc = s.pos[n == 0 ? 0 : N - n];
+    float2* dst = ubase + (long)n * N * N;
+    for (int g = lane; g < cnt; g += 32) {
+      const float2 zk = s.data[g * ld + pk];
+      const float2 zc = s.data[g * ld + pc];
+      float4 o;
+      o.x = 0.5f * (zk.x + zc.x);
+      o.y = 0.5f * (zk.y - zc.y);
+      o.z = 0.5f * (zk.y + zc.y);
+      o.w = -0.5f * (zk.x - zc.x);
+      *reinterpret_cast<float4*>(dst + 2 * g) = o;
+    }
   }
 }
 
@@ -127,36 +159,53 @@ struct FwdAlphaParams {
   FftDev fft;
 };
 
+// G divides N: all rows of a block share (z, n) and cover consecutive betas.
 S2C_KERNEL(so3_fwd_alpha, FwdAlphaParams) {
   const int N = p.N, ld = N + 1;
   FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
+  const int warp = ctx.tid >> 5, lane = ctx.tid & 31, nwarps = ctx.nthr >> 5;
   const long row0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
   if (p.in_real) {
-    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-      const int g = it / N, a = it - g * N;
-      s.data[g * ld + a] = make_float2(p.in[(row0 + g) * N + a], 0.f);
-    }
+    for (int g = warp; g < cnt; g += nwarps)
+      for (int a = lane; a < N; a += 32)
+        s.data[g * ld + a] = make_float2(p.in[(row0 + g) * N + a], 0.f);
   } else {
-    const float2* in2 = reinterpret_cast<const float2*>(p.in);
-    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-      const int g = it / N, a = it - g * N;
-      s.data[g * ld + a] = in2[(row0 + g) * N + a];
+    // contiguous run of cnt rows: 16-byte loads (two complex numbers), four in flight per thread
+    const float4* src = reinterpret_cast<const float4*>(p.in + (row0 * N) * 2);
+    const int n2 = N / 2, total = cnt * n2;  // N is even
+    for (int base = ctx.tid; base < total; base += 4 * ctx.nthr) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total) v[u] = src[idx];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total) {
+          const int g = idx / n2, a2 = idx - g * n2;
+          s.data[g * ld + 2 * a2] = make_float2(v[u].x, v[u].y);
+          s.data[g * ld + 2 * a2 + 1] = make_float2(v[u].z, v[u].w);
+        }
+      }
     }
   }
   ctx.sync();
   fft_rows<-1>(ctx, s, p.fft.desc, cnt, ld);
   const int nm = 2 * p.K - 1;
-  for (int it = ctx.tid; it < cnt * nm; it += ctx.nthr) {
-    const int mi = it / cnt, g = it - mi * cnt;
+  const long zn = row0 / N;
+  const int beta0 = (int)(row0 - zn * N);
+  const int n = (int)(zn % p.Kn);
+  const long z = zn / p.Kn;
+  float2* vbase = p.v + (((long)n * nm) * p.nbatch + z) * N + beta0;
+  for (int mi = warp; mi < nm; mi += nwarps) {
     const int m = mi - (p.K - 1);
-    const long r = row0 + g;
-    const int beta = (int)(r % N);
-    const long zn = r / N;
-    const int n = (int)(zn % p.Kn);
-    const long z = zn / p.Kn;
-    p.v[(((long)n * nm + mi) * p.nbatch + z) * N + beta] = s.data[g * ld + s.pos[m < 0 ? m + N : m]];
+    const int pm = s.pos[m < 0 ? m + N : m];
+    float2* dst = vbase + (long)mi * p.nbatch * N;
+    for (int g = lane; g < cnt; g += 32) dst[g] = s.data[g * ld + pm];
   }
 }
 
@@ -311,41 +360,52 @@ struct InvAlphaParams {
   FftDev fft;
 };
 
+// G divides N: all rows of a block share (z, n) and cover consecutive betas.
 S2C_KERNEL(so3_inv_alpha, InvAlphaParams) {
   const int N = p.N, ld = N + 1;
   FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
+  const int warp = ctx.tid >> 5, lane = ctx.tid & 31, nwarps = ctx.nthr >> 5;
   const long row0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.nrows - row0) < p.G ? (p.nrows - row0) : p.G);
   for (int it = ctx.tid; it < cnt * ld; it += ctx.nthr) s.data[it] = make_float2(0.f, 0.f);
   ctx.sync();
   const int nm = 2 * p.K - 1;
-  for (int it = ctx.tid; it < cnt * nm; it += ctx.nthr) {
-    const int mi = it / cnt, g = it - mi * cnt;
-    const int m = mi - (p.K - 1);
-    const long r = row0 + g;
-    const int beta = (int)(r % N);
-    const long zn = r / N;
-    const int n = (int)(zn % p.Kn);
-    const long z = zn / p.Kn;
-    if (p.herm_n0 && n == 0 && m < 0) continue;
-    const float2 v = p.s[(((long)n * nm + mi) * p.nbatch + z) * N + beta];
-    s.data[g * ld + (m < 0 ? m + N : m)] = v;
-    if (p.herm_n0 && n == 0 && m > 0) s.data[g * ld + N - m] = make_float2(v.x, -v.y);
+  const long zn = row0 / N;
+  const int beta0 = (int)(row0 - zn * N);
+  const int n = (int)(zn % p.Kn);
+  const long z = zn / p.Kn;
+  const bool herm = p.herm_n0 && n == 0;  // only m >= 0 is stored; m < 0 is the conjugate
+  const float2* sbase = p.s + (((long)n * nm) * p.nbatch + z) * N + beta0;
+  for (int mi0 = warp; mi0 < nm; mi0 += 4 * nwarps) {   // four independent loads per lane in flight
+    for (int g = lane; g < cnt; g += 32) {
+      float2 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int mi = mi0 + u * nwarps;
+        const int m = mi - (p.K - 1);
+        if (mi < nm && !(herm && m < 0)) v[u] = sbase[(long)mi * p.nbatch * N + g];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int mi = mi0 + u * nwarps;
+        const int m = mi - (p.K - 1);
+        if (mi < nm && !(herm && m < 0)) {
+          s.data[g * ld + (m < 0 ? m + N : m)] = v[u];
+          if (herm && m > 0) s.data[g * ld + N - m] = make_float2(v[u].x, -v[u].y);
+        }
+      }
+    }
   }
   ctx.sync();
   fft_rows<+1>(ctx, s, p.fft.desc, cnt, ld);
   if (p.out_real) {
-    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-      const int g = it / N, a = it - g * N;
-      p.out[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]].x;
-    }
+    for (int g = warp; g < cnt; g += nwarps)
+      for (int a = lane; a < N; a += 32) p.out[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]].x;
   } else {
     float2* out2 = reinterpret_cast<float2*>(p.out);
-    for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-      const int g = it / N, a = it - g * N;
-      out2[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]];
-    }
+    for (int g = warp; g < cnt; g += nwarps)
+      for (int a = lane; a < N; a += 32) out2[(row0 + g) * N + a] = s.data[g * ld + s.pos[a]];
   }
 }
 
@@ -364,42 +424,55 @@ struct InvGammaParams {
   FftDev fft;
 };
 
+// G divides b: all row pairs of a block belong to one (z, beta) plane.
 S2C_KERNEL(so3_inv_gamma, InvGammaParams) {
   const int N = p.N, ld = N + 1;
   FftSmem s = fft_smem_carve(smem, N, p.G);
   fft_smem_load_tables(ctx, s, p.fft);
+  const int warp = ctx.tid >> 5, lane = ctx.tid & 31, nwarps = ctx.nthr >> 5;
   const long pair0 = (long)ctx.bid * p.G;
   const int cnt = (int)((p.npairs - pair0) < p.G ? (p.npairs - pair0) : p.G);
   for (int it = ctx.tid; it < cnt * ld; it += ctx.nthr) s.data[it] = make_float2(0.f, 0.f);
   ctx.sync();
-  for (int it = ctx.tid; it < cnt * p.K; it += ctx.nthr) {
-    const int n = it / cnt, g = it - n * cnt;
-    const long pid = pair0 + g;
-    const int pp = (int)(pid % p.b);
-    const long zb = pid / p.b;
-    const int beta = (int)(zb % N);
-    const long z = zb / N;
-    const float4 tv =
-        *reinterpret_cast<const float4*>(p.t + ((z * p.K + n) * N + beta) * N + 2 * pp);
-    if (n == 0) {
-      // T[alpha][0] is real for a Hermitian spectrum; its rounding-level imaginary part is dropped
-      s.data[g * ld] = make_float2(tv.x, tv.z);
-    } else {
-      s.data[g * ld + n] = make_float2(tv.x - tv.w, tv.y + tv.z);       // T1 + i T2
-      s.data[g * ld + N - n] = make_float2(tv.x + tv.w, tv.z - tv.y);   // conj(T1) + i conj(T2)
+  const long zb = pair0 / p.b;
+  const int pp0 = (int)(pair0 - zb * p.b);
+  const int beta = (int)(zb % N);
+  const long z = zb / N;
+  const float2* tbase = p.t + ((z * p.K) * N + beta) * (long)N + 2 * pp0;
+  for (int n0 = warp; n0 < p.K; n0 += 4 * nwarps) {   // four independent loads per lane in flight
+    for (int g = lane; g < cnt; g += 32) {
+      float4 tv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int n = n0 + u * nwarps;
+        if (n < p.K) tv[u] = *reinterpret_cast<const float4*>(tbase + (long)n * N * N + 2 * g);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int n = n0 + u * nwarps;
+        if (n >= p.K) continue;
+        const float4 t4 = tv[u];
+        if (n == 0) {
+          // T[alpha][0] is real for a Hermitian spectrum; its rounding-level imaginary part is dropped
+          s.data[g * ld] = make_float2(t4.x, t4.z);
+        } else {
+          s.data[g * ld + n] = make_float2(t4.x - t4.w, t4.y + t4.z);       // T1 + i T2
+          s.data[g * ld + N - n] = make_float2(t4.x + t4.w, t4.z - t4.y);   // conj(T1) + i conj(T2)
+        }
+      }
     }
   }
   ctx.sync();
   fft_rows<+1>(ctx, s, p.fft.desc, cnt, ld);
-  for (int it = ctx.tid; it < cnt * N; it += ctx.nthr) {
-    const int g = it / N, gam = it - g * N;
-    const long pid = pair0 + g;
-    const float2 v = s.data[g * ld + s.pos[gam]];
-    float add = 0.f;
-    if (p.bias) add = p.bias[(p.z0 + pid / ((long)p.b * N)) % p.nfeat];
-    const long e = pid * 2 * N + gam;
-    p.out[e * p.out_stride + p.out_off] = v.x + add;
-    p.out[(e + N) * p.out_stride + p.out_off] = v.y + add;
+  float add = 0.f;
+  if (p.bias) add = p.bias[(p.z0 + z) % p.nfeat];
+  for (int g = warp; g < cnt; g += nwarps) {
+    const long e0 = (pair0 + g) * 2 * N;
+    for (int gam = lane; gam < N; gam += 32) {
+      const float2 v = s.data[g * ld + s.pos[gam]];
+      p.out[(e0 + gam) * p.out_stride + p.out_off] = v.x + add;
+      p.out[(e0 + N + gam) * p.out_stride + p.out_off] = v.y + add;
+    }
   }
 }
 
