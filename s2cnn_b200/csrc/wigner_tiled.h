@@ -37,19 +37,95 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
   float2* Vs = reinterpret_cast<float2*>(Ws + (size_t)N * LW);  // [N][ZP]   (transposed tile)
   const int LT = (L + 3) / 4, Z2 = (zc + 1) / 2;
   const float* panel = p.pan.data + p.pan.off[pair];
-  for (int it = ctx.tid; it < LT * 4 * N; it += ctx.nthr) {
-    const int l = it / N, bt = it - l * N;
-    Ws[bt * LW + l] = l < L ? panel[it] : 0.f;
+  // panel and batch tile, transposed into [beta][.]; 16-byte loads, four in flight per thread
+  {
+    const float4* src = reinterpret_cast<const float4*>(panel);   // panel offsets are multiples of N
+    const int n4 = N / 4, total = LT * 4 * n4;
+    for (int base = ctx.tid; base < total; base += 4 * ctx.nthr) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < total && idx / n4 < L) v[u] = src[idx];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total) {
+          const int l = idx / n4, bt = 4 * (idx - l * n4);
+          Ws[(bt + 0) * LW + l] = v[u].x;
+          Ws[(bt + 1) * LW + l] = v[u].y;
+          Ws[(bt + 2) * LW + l] = v[u].z;
+          Ws[(bt + 3) * LW + l] = v[u].w;
+        }
+      }
+    }
   }
   const int nm = 2 * p.K - 1, mi = m + p.K - 1;
-  const float2* vsrc = p.v + (((long)n * nm + mi) * p.nbatch + z0) * N;
-  for (int it = ctx.tid; it < Z2 * 2 * N; it += ctx.nthr) {
-    const int zz = it / N, bt = it - zz * N;
-    Vs[bt * ZP + zz] = zz < zc ? vsrc[it] : make_float2(0.f, 0.f);
+  {
+    const float4* src = reinterpret_cast<const float4*>(p.v + (((long)n * nm + mi) * p.nbatch + z0) * N);
+    const int n2 = N / 2, total = Z2 * 2 * n2;
+    for (int base = ctx.tid; base < total; base += 4 * ctx.nthr) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < total && idx / n2 < zc) v[u] = src[idx];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * ctx.nthr;
+        if (idx < total) {
+          const int zz = idx / n2, bt = 2 * (idx - zz * n2);
+          Vs[bt * ZP + zz] = make_float2(v[u].x, v[u].y);
+          Vs[(bt + 1) * ZP + zz] = make_float2(v[u].z, v[u].w);
+        }
+      }
+    }
   }
   ctx.sync();
   const float fudge = ((m - n) & 1) ? -1.f : 1.f;
   const bool self = (m == 0 && n == 0);
+  if (LT * Z2 < ctx.nthr) {
+    // few degrees for this pair: 4 x 1 tiles so that more threads share the beta loop
+    for (int tile = ctx.tid; tile < LT * zc; tile += ctx.nthr) {
+      const int tl = tile / zc, zz = tile - tl * zc;
+      float ar[4] = {0.f, 0.f, 0.f, 0.f}, ai[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* wp = Ws + 4 * tl;
+      const float2* vp = Vs + zz;
+      for (int bt = 0; bt < N; ++bt) {
+        const float4 w4 = *reinterpret_cast<const float4*>(wp + bt * LW);
+        const float2 v2 = vp[bt * ZP];
+        ar[0] = fmaf(w4.x, v2.x, ar[0]); ai[0] = fmaf(w4.x, v2.y, ai[0]);
+        ar[1] = fmaf(w4.y, v2.x, ar[1]); ai[1] = fmaf(w4.y, v2.y, ai[1]);
+        ar[2] = fmaf(w4.z, v2.x, ar[2]); ai[2] = fmaf(w4.z, v2.y, ai[2]);
+        ar[3] = fmaf(w4.w, v2.x, ar[3]); ai[3] = fmaf(w4.w, v2.y, ai[3]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int li = 4 * tl + i;
+        if (li >= L) continue;
+        const int l = lmin + li;
+        float2* o1 = p.out + so3_row(l, m, n) * p.out_zstride + z0 + zz;
+        float2* o2 = p.out + so3_row(l, -m, -n) * p.out_zstride + z0 + zz;
+        const float re = ar[i], im = ai[i];
+        if (p.mode == kSo3Real) {
+          *o1 = make_float2(re, im);
+          if (!self) *o2 = make_float2(fudge * re, -fudge * im);
+        } else {
+          float2 c = *o1;
+          *o1 = make_float2(c.x - im, c.y + re);
+          if (!self) {
+            c = *o2;
+            *o2 = make_float2(c.x + fudge * im, c.y + fudge * re);
+          }
+        }
+      }
+    }
+    return;
+  }
   for (int tile = ctx.tid; tile < LT * Z2; tile += ctx.nthr) {
     const int tl = tile / Z2, tz = tile - tl * Z2;
     float ar[4][2], ai[4][2];
@@ -118,7 +194,20 @@ S2C_KERNEL(so3_inv_wigner_t, InvWignerParams) {
   float2* Xs = reinterpret_cast<float2*>(Ws + (size_t)p.pan.nl * N);      // [L][ZP]
   const int Z2 = (zc + 1) / 2;
   const float* panel = p.pan.data + p.pan.off[pair];
-  for (int it = ctx.tid; it < L * N; it += ctx.nthr) Ws[it] = panel[it];
+  {
+    const float4* src = reinterpret_cast<const float4*>(panel);
+    float4* dst4 = reinterpret_cast<float4*>(Ws);
+    const int total = L * N / 4;
+    for (int base = ctx.tid; base < total; base += 4 * ctx.nthr) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (base + u * ctx.nthr < total) v[u] = src[base + u * ctx.nthr];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (base + u * ctx.nthr < total) dst4[base + u * ctx.nthr] = v[u];
+    }
+  }
   const float fudge = ((m - n) & 1) ? -1.f : 1.f;
   for (int it = ctx.tid; it < L * Z2 * 2; it += ctx.nthr) {
     const int li = it / (Z2 * 2), zz = it - li * (Z2 * 2);
