@@ -167,6 +167,47 @@ inline int launch_impl(K kernel, const char* kname, long grid, int block, size_t
 #define S2C_LAUNCH(name, grid, block, smem, stream, params) \
   s2c::launch_impl(name, #name, (long)(grid), (int)(block), (size_t)(smem), stream, params)
 
+namespace s2c {
+// ---- asynchronous bulk copy global -> shared (TMA, 1-D) completing on an mbarrier -------------
+// dst, src and bytes must be multiples of 16.  One thread initialises the barrier and issues the
+// copies; every thread waits with bulk_wait (bounded: returns false if the copy never lands, in
+// which case the caller reads the data from global memory instead).
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void bulk_barrier_init(unsigned long long* bar) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(bar)));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_load_issue(void* dst, const void* src, unsigned bytes,
+                                                unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ bool bulk_wait(const Ctx&, unsigned long long* bar, unsigned parity) {
+  const unsigned addr = smem_u32(bar);
+  for (int spin = 0; spin < (1 << 20); ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (spin > 32) __nanosleep(32);
+  }
+  return false;
+}
+}  // namespace s2c
+
 #else
 // ------------------------------------------------------------------------------------------
 // Host emulation backend (test-only)
@@ -319,6 +360,19 @@ inline int emu_launch(const char* kname, long grid, int block, size_t smem, cons
   inline void name##_impl::run(const s2c::Ctx& ctx, const P& p, unsigned char* smem)
 
 #define S2C_KERNEL_BOUNDS(name, P, MAXT, MINB) S2C_KERNEL(name, P)
+
+namespace s2c {
+// Host stand-ins of the bulk-copy helpers: the copy happens at issue time, the wait is a block
+// barrier (every thread of the block calls it at the same point).
+inline void bulk_barrier_init(unsigned long long*) {}
+inline void bulk_load_issue(void* dst, const void* src, unsigned bytes, unsigned long long*) {
+  std::memcpy(dst, src, bytes);
+}
+inline bool bulk_wait(const Ctx& ctx, unsigned long long*, unsigned) {
+  ctx.sync();
+  return true;
+}
+}  // namespace s2c
 
 #define S2C_LAUNCH(name, grid, block, smem, stream, params)                                  \
   s2c::emu_launch<name##_impl>(#name, (long)(grid), (int)(block), (size_t)(smem), params)

@@ -24,8 +24,6 @@
 
 namespace s2c {
 
-constexpr int kFusedZG = 4;
-constexpr int kMaxBG = 8;   // upper bound of the betas per group (register accumulators)
 
 S2C_D void rowmap_unpack(int packed, int& l, int& m, int& n) {
   l = packed & 0xff;
@@ -73,7 +71,14 @@ struct so3_inv_fused_impl {
     float2* tw = reinterpret_cast<float2*>(smem);
     float2* Xh = tw + N;                              // [nrows][ZG]
     int4* pinfo = reinterpret_cast<int4*>(Xh + (size_t)p.nrows * ZG);    // [npairs]
-    float2* planes = reinterpret_cast<float2*>(pinfo + p.pan.npairs);     // [ZG * BG][N][KP]
+    float* Wg = reinterpret_cast<float*>(pinfo + p.pan.npairs);           // [nrows][BG] of one group
+    unsigned long long* wbar = reinterpret_cast<unsigned long long*>(Wg + p.pan.g_stride);
+    float2* planes = reinterpret_cast<float2*>(wbar + 2);                 // [ZG * BG][N][KP]
+    const unsigned wbytes = (unsigned)p.pan.g_stride * sizeof(float);
+    if (ctx.tid == 0) {
+      bulk_barrier_init(wbar);
+      bulk_load_issue(Wg, p.pan.data_g, wbytes, wbar);   // Wigner slice of the first beta group
+    }
     const int plane_sz = p.PS;
     const long z0 = (long)ctx.bid * ZG;
     const int zc = (int)((p.nbatch - z0) < ZG ? (p.nbatch - z0) : ZG);
@@ -115,17 +120,22 @@ struct so3_inv_fused_impl {
 
     for (int bg0 = 0; bg0 < N; bg0 += p.BG) {
       const int bc = (N - bg0) < p.BG ? (N - bg0) : p.BG;
-      // ---- Wigner contraction over l: one (pair, beta) per work item, ZG accumulators -------
+      // ---- Wigner contraction over l: one (pair, beta) per work item, ZG accumulators.  The
+      //      group's slice of the table was brought into shared memory by an asynchronous bulk
+      //      copy issued one group earlier; if it did not land in time, read global memory. ----
+      const int grp = bg0 / p.BG;
+      const bool landed = bulk_wait(ctx, wbar, (unsigned)(grp & 1));
+      const float* wslice = landed ? Wg : p.pan.data_g + (size_t)grp * p.pan.g_stride;
       for (int it = ctx.tid; it < p.pan.npairs * bc; it += ctx.nthr) {
         const int pr = it / bc, bi = it - pr * bc;
         const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
-        const float* w = p.pan.data + (long)info.x * N + bg0 + bi;
+        const float* w = wslice + info.x * p.BG + bi;
         const float2* xs = Xh + info.x * ZG;
         float2 acc[ZG];
 #pragma unroll
         for (int z = 0; z < ZG; ++z) acc[z] = make_float2(0.f, 0.f);
         for (int li = 0; li < info.y; ++li) {
-          const float wv = w[li * N];
+          const float wv = w[li * p.BG];
 #pragma unroll
           for (int z = 0; z < ZG; ++z) {
             const float2 xv = xs[li * ZG + z];
@@ -143,6 +153,8 @@ struct so3_inv_fused_impl {
         }
       }
       ctx.sync();
+      if (ctx.tid == 0 && bg0 + p.BG < N)   // every thread is done with this slice: fetch the next
+        bulk_load_issue(Wg, p.pan.data_g + (size_t)(grp + 1) * p.pan.g_stride, wbytes, wbar);
       // ---- column FFTs m -> alpha: one thread per (z, beta, n) ------------------------------
       for (int it = ctx.tid; it < ZG * bc * K; it += ctx.nthr) {
         const int n = it % K, zb = it / K;
@@ -419,7 +431,6 @@ __global__ void __launch_bounds__(256) so3_fwd_fused(const FwdFusedParams p) {
     default: rc = s2c::fail(s2c::S2C_ERR_UNSUPPORTED, "no fused kernel for this length");    \
   }
 
-constexpr int kFusedMaxN = 32;
 
 // Row stride of a plane in complex numbers: >= N/2 (a row must hold N floats) and odd, so that
 // threads walking down a column of rows fall into distinct shared-memory banks.
@@ -431,18 +442,10 @@ inline int fused_plane_stride(int N, int K) {
   while (ps % 16 != K % 16) ++ps;
   return ps;
 }
-// Betas per group: the largest divisor of N that keeps the per-group transform count
-// (ZG * BG * N/2 threads, one transform each) within one pass of a 256-thread block.
-inline int fused_bg(int N) {
-  int best = 1;
-  for (int d = 1; d <= N; ++d)
-    if (N % d == 0 && d <= kMaxBG && kFusedZG * d * (N / 2) <= 256) best = d;
-  return best;
-}
 inline size_t fused_smem_bytes(int N, int nrows) {
   const int K = N / 2;  // upper bound of the pair count: so3_npairs(K)
   return (size_t)N * sizeof(float2) + (size_t)nrows * kFusedZG * sizeof(float2) +
-         (size_t)so3_npairs(K) * sizeof(int4) +
+         (size_t)so3_npairs(K) * sizeof(int4) + ((size_t)nrows * fused_bg(N) + 4) * sizeof(float) + 16 +
          (size_t)kFusedZG * fused_bg(N) * (N * fused_kp(N) + 16) * sizeof(float2);
 }
 

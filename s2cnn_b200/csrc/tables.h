@@ -41,7 +41,26 @@ struct PanelsDev {
   const float* data;        // device
   const long long* off;     // device, npairs + 1 offsets (in floats)
   const int* rowmap;        // device, nrows entries: l | (m + 128) << 8 | n << 16 of each panel row
+  // Copy for the single-kernel path (only when nbeta <= 32, else null): the same values regrouped
+  // by beta group, data_g[g * g_stride + row * g_bg + bi] = data[row * nbeta + g * g_bg + bi], so
+  // that the slice a block needs for one beta group is one contiguous, 16-byte aligned run.
+  const float* data_g;
+  int g_bg;                 // betas per group
+  int g_stride;             // floats per group slice (multiple of 4)
 };
+
+// ---- configuration of the single-kernel path (shared by the table builder and the kernels) ----
+constexpr int kFusedZG = 4;    // batch elements per block
+constexpr int kMaxBG = 8;      // upper bound of the betas per group
+constexpr int kFusedMaxN = 32;
+// Betas per group: the largest divisor of N that keeps the per-group transform count
+// (ZG * BG * N/2 threads, one transform each) within one pass of a 256-thread block.
+inline int fused_bg(int N) {
+  int best = 1;
+  for (int d = 1; d <= N; ++d)
+    if (N % d == 0 && d <= kMaxBG && kFusedZG * d * (N / 2) <= 256) best = d;
+  return best;
+}
 
 S2C_HD int so3_npairs(int K) { return K + (K - 1) * (2 * K - 1); }
 S2C_HD int so3_pair_index(int m, int n, int K) {
@@ -158,6 +177,25 @@ class TableCache {
       rc = dev_upload(drm, rowmap.data(), rowmap.size() * sizeof(int));
       if (rc) return rc;
       PanelsDev pd;
+      pd.data_g = nullptr;
+      pd.g_bg = 0;
+      pd.g_stride = 0;
+      if (!s2 && 2 * b_beta <= kFusedMaxN) {
+        const int nbeta = 2 * b_beta, bg = fused_bg(nbeta), nrows = (int)rowmap.size();
+        const int stride = (nrows * bg + 3) / 4 * 4;
+        std::vector<float> grouped((size_t)stride * (nbeta / bg), 0.f);
+        for (int g = 0; g < nbeta / bg; ++g)
+          for (int r = 0; r < nrows; ++r)
+            for (int bi = 0; bi < bg; ++bi)
+              grouped[(size_t)g * stride + (size_t)r * bg + bi] = data[(size_t)r * nbeta + g * bg + bi];
+        void* dg = dev_alloc(grouped.size() * sizeof(float));
+        if (!dg) return fail(S2C_ERR_CUDA, "table allocation failed");
+        rc = dev_upload(dg, grouped.data(), grouped.size() * sizeof(float));
+        if (rc) return rc;
+        pd.data_g = (const float*)dg;
+        pd.g_bg = bg;
+        pd.g_stride = stride;
+      }
       pd.nrows = (int)rowmap.size();
       pd.rowmap = (const int*)drm;
       pd.nbeta = 2 * b_beta;
@@ -199,6 +237,7 @@ class TableCache {
       dev_free((void*)kv.second.data);
       dev_free((void*)kv.second.off);
       dev_free((void*)kv.second.rowmap);
+      if (kv.second.data_g) dev_free((void*)kv.second.data_g);
     }
     for (auto& kv : quad_) dev_free((void*)kv.second);
     fft_.clear();
