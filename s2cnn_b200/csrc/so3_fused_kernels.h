@@ -91,30 +91,49 @@ struct so3_inv_fused_impl {
       pinfo[pr] = make_int4((int)(p.pan.off[pr] / N), K - lmin, m < 0 ? m + N : m, n);
     }
     // symmetrised half spectrum  Xs = (X[l,m,n] + (-1)^(m-n) conj X[l,-m,-n]) / 2
-    for (int it = ctx.tid; it < p.nrows * ZG; it += ctx.nthr) {
-      const int r = it / ZG, zz = it - r * ZG;
-      float2 v = make_float2(0.f, 0.f);
-      if (zz < zc) {
-        int l, m, n;
-        rowmap_unpack(p.pan.rowmap[r], l, m, n);
-        float2 a, b;
-        if (p.mode == kS2Product) {
-          const int z = (int)(z0 + zz);
-          const int i = z / p.s2_fout, j = z - i * p.s2_fout;
-          a = s2_product_entry(p, l, m, n, i, j);
-          b = s2_product_entry(p, l, -m, -n, i, j);
-        } else {
-          a = p.x[so3_row(l, m, n) * p.x_zstride + z0 + zz];
-          b = p.x[so3_row(l, -m, -n) * p.x_zstride + z0 + zz];
+    // (four work items per thread at a time so that eight independent row loads are in flight)
+    for (int base = ctx.tid; base < p.nrows * ZG; base += 4 * ctx.nthr) {
+      int packed[4];
+      float2 a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int it = base + u * ctx.nthr;
+        packed[u] = it < p.nrows * ZG ? p.pan.rowmap[it / ZG] : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int it = base + u * ctx.nthr;
+        const int zz = it % ZG;
+        a[u] = make_float2(0.f, 0.f);
+        b[u] = make_float2(0.f, 0.f);
+        if (it < p.nrows * ZG && zz < zc) {
+          int l, m, n;
+          rowmap_unpack(packed[u], l, m, n);
+          if (p.mode == kS2Product) {
+            const int z = (int)(z0 + zz);
+            const int i = z / p.s2_fout, j = z - i * p.s2_fout;
+            a[u] = s2_product_entry(p, l, m, n, i, j);
+            b[u] = s2_product_entry(p, l, -m, -n, i, j);
+          } else {
+            a[u] = p.x[so3_row(l, m, n) * p.x_zstride + z0 + zz];
+            b[u] = p.x[so3_row(l, -m, -n) * p.x_zstride + z0 + zz];
+          }
         }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int it = base + u * ctx.nthr;
+        if (it >= p.nrows * ZG) continue;
+        int l, m, n;
+        rowmap_unpack(packed[u], l, m, n);
+        float2 av = a[u], bv = b[u];
         if (p.mode == kSo3RotI) {
-          a = make_float2(a.y, -a.x);
-          b = make_float2(b.y, -b.x);
+          av = make_float2(av.y, -av.x);
+          bv = make_float2(bv.y, -bv.x);
         }
         const float fudge = ((m - n) & 1) ? -1.f : 1.f;
-        v = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
+        Xh[it] = make_float2(0.5f * (av.x + fudge * bv.x), 0.5f * (av.y - fudge * bv.y));
       }
-      Xh[it] = v;
     }
     ctx.sync();
 
