@@ -1,0 +1,48 @@
+"""Small, fixed workloads for profiler captures of single kernels.
+
+    python -m s2cnn_b200.profile_cases <case>
+
+Each case runs one op a few times on seeded synthetic data sized for a capture that ends by itself
+within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hundred MB at most):
+
+    inv10   so3_rifft, b = 10, 5120 signals          (kernel so3_inv_fused<20>)
+    fwd10   so3_rfft,  b = 10 -> 6, 5120 signals     (kernel so3_fwd_fused<20>)
+    mm      so3_mm, nl = 6, batch 256, 20 -> 40      (kernel so3_mm_tc_kernel)
+    fft64   so3_rfft + so3_rifft, b = 64, 8 signals  (general-path kernels)
+"""
+import sys
+
+import torch
+
+from .ops import cuda_ops, so3_nspec
+
+
+def main(which):
+    ops = cuda_ops()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    if which == "inv10":
+        s = torch.randn(so3_nspec(10), 5120, 2, device=dev)
+        for _ in range(3):
+            ops.so3_rifft(s)
+    elif which == "fwd10":
+        x = torch.randn(5120, 20, 20, 20, device=dev)
+        for _ in range(3):
+            ops.so3_rfft(x, b_out=6)
+    elif which == "mm":
+        x = torch.randn(so3_nspec(6), 256, 20, 2, device=dev)
+        y = torch.randn(so3_nspec(6), 20, 40, 2, device=dev)
+        for _ in range(3):
+            ops.so3_mm(x, y)
+    elif which == "fft64":
+        x = torch.randn(8, 128, 128, 128, device=dev)
+        for _ in range(2):
+            ops.so3_rifft(ops.so3_rfft(x))
+    else:
+        raise SystemExit(__doc__)
+    torch.cuda.synchronize()
+    print("ok")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "")
