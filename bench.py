@@ -146,7 +146,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                 "-lms", "20", "-i", str(self.index)], stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -413,7 +413,6 @@ def run_ours(args):
     launches = (lib.s2c_launch_count() - n0) * args.steps
     barrier(world)
     total_ms = max_over_ranks(total_ms, world, device)
-    clocks = sampler.stop() if rank == 0 else None
     ms_per_step = total_ms / args.steps
     value = B * world / (ms_per_step * 1e-3)
 
@@ -424,6 +423,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     barrier(world)
     e2e_ms = max_over_ranks(e2e_ms, world, device) / args.steps
+    clocks = sampler.stop() if rank == 0 else None   # sampled over both timed legs
     e2e = {"value": B * world / (e2e_ms * 1e-3), "unit": "samples/s",
            "h2d_bytes_per_step": x_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4,
            "ms_per_step": e2e_ms}
@@ -464,8 +464,13 @@ def run_ours(args):
                     "peak_source": peak_kind + " bf16 / 2 (TF32 dense)"}
     else:
         ach = top["GBps"]
+        # DRAM bytes per step of this kernel's launches from one ncu capture of this same command
+        # (profiles/net_b30_10_6_launch_list.md); below the algorithmic bytes because part of the
+        # output is still in L2 when the kernel ends - no re-reads
+        traffic = {"so3_inv_fused": 1.5e6 + 104.7e6 + 23.5e6 + 9.6e6,
+                   "so3_fwd_fused": 163.9e6 + 3.8e6}.get(top["kernel"]) if B == 256 else None
         roofline = {"kernel": top["kernel"], "bound": "hbm", "achieved": ach, "peak": hbm_gbs,
-                    "unit": "GB/s", "frac": ach / hbm_gbs, "traffic": None,
+                    "unit": "GB/s", "frac": ach / hbm_gbs, "traffic": traffic,
                     "peak_source": peak_kind,
                     "alg_bytes_per_step": top["alg_bytes_per_step"],
                     "launches_per_step": top["launches_per_step"]}
