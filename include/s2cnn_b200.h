@@ -183,6 +183,18 @@ int s2c_so3_integrate(const float* x, float* out, long n, int b, int relu, void*
 int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n, int b, int relu,
                                void* stream);
 
+/* ---- rotation of a signal on SO(3) ------------------------------------------------------------ */
+/* HOST generator: out = concatenation over l < b of U^l[m, n] = exp(i m alpha) d^l_mn(beta)
+ * exp(i n gamma), interleaved complex floats, b(4b^2-1)/3 entries.  Replaces the lie_learn
+ * wigner_D_matrix call of __setup_so3_rotation, s2cnn/soft/so3_rotation.py:51-62. */
+int s2c_so3_rotation_matrices(int b, double alpha, double beta, double gamma, float* out);
+/* DEVICE: z[l,m,n,c] = sum_k conj(U^l[m,k]) x[l,k,n,c]   (adjoint == 0), or the transposed product
+ * gx[l,k,n,c] = sum_m U^l[m,k] gz[l,m,n,c]               (adjoint != 0), for spectra
+ * [b(4b^2-1)/3, nbatch, 2].  Replaces the per-degree complex_mm loop of so3_rotation,
+ * s2cnn/soft/so3_rotation.py:22-41 (and, with adjoint, its autograd). */
+int s2c_so3_rotate_spectrum(const float* U, const float* x, float* z, int b, long nbatch,
+                            int adjoint, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -58,6 +58,8 @@ _SIGNATURES = {
     "s2c_rft_backward": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
     "s2c_so3_integrate": (c_int, [_P, _P, c_long, c_int, c_int, _P]),
     "s2c_so3_integrate_backward": (c_int, [_P, _P, _P, c_long, c_int, c_int, _P]),
+    "s2c_so3_rotation_matrices": (c_int, [c_int, c_double, c_double, c_double, _P]),
+    "s2c_so3_rotate_spectrum": (c_int, [_P, _P, _P, c_int, c_long, c_int, _P]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -235,4 +235,22 @@ inline CgemmParams mm_params(bool so3, int op, int nl, int nb, int fi, int fo) {
   return p;
 }
 
+// Rotation of an SO(3) spectrum by block-diagonal Wigner-D matrices (s2cnn/soft/so3_rotation.py:22-41):
+//   adjoint = 0:  z[l,m,n,b]  = sum_k conj(U^l[m,k]) x[l,k,n,b]
+//   adjoint = 1:  gx[l,k,n,b] = sum_m      U^l[m,k]  gz[l,m,n,b]      (transpose of the above)
+// U is the concatenation over l of the (2l+1) x (2l+1) matrices, x / z are [nspec3, nbatch].
+inline CgemmParams rotation_params(int nl, long nbatch, int adjoint) {
+  CgemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.nl = nl;
+  p.rL = 1; p.R2 = 1; p.cL = 1; p.C2 = (int)nbatch; p.kL = 1; p.K2 = 1;
+  p.a.base_unit = 1;
+  if (!adjoint) { p.a.o1L = 1; p.a.o2c = 1; p.a_fast_k = 1; p.conjA = 1; }
+  else          { p.a.o1c = 1; p.a.o2L = 1; p.a_fast_k = 0; p.conjA = 0; }
+  p.b.base_unit = nbatch; p.b.o1L = nbatch; p.b.o2c = nbatch; p.b.i2 = 1;
+  p.c = p.b;
+  p.conjB = 0; p.b_fast_k = 0;
+  return p;
+}
+
 }  // namespace s2c

@@ -679,6 +679,34 @@ int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n
   return S2C_LAUNCH(so3_integrate_bwd, blocks, 256, 0, as_stream(st), p);
 }
 
+int s2c_so3_rotation_matrices(int b, double alpha, double beta, double gamma, float* out) {
+  if (b < 1 || !out) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rotation_matrices: bad argument");
+  std::vector<double> col(b + 1);
+  for (int m = -(b - 1); m <= b - 1; ++m)
+    for (int n = -(b - 1); n <= b - 1; ++n) {
+      const int l0 = wigner_d_degrees(m, n, beta, b, col.data());
+      const double ph = m * alpha + n * gamma;
+      const double cr = std::cos(ph), ci = std::sin(ph);
+      for (int l = l0; l < b; ++l) {
+        const long idx = so3_offset(l) + (long)(m + l) * (2 * l + 1) + (n + l);
+        out[2 * idx] = (float)(cr * col[l - l0]);
+        out[2 * idx + 1] = (float)(ci * col[l - l0]);
+      }
+    }
+  return S2C_OK;
+}
+
+int s2c_so3_rotate_spectrum(const float* U, const float* x, float* z, int b, long nbatch,
+                            int adjoint, void* st) {
+  if (!U || !x || !z || b < 1 || nbatch < 1 || nbatch > 0x7fffffffL / (2 * b))
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rotate_spectrum: bad argument");
+  CgemmParams p = rotation_params(b, nbatch, adjoint ? 1 : 0);
+  p.A = (const float2*)U;
+  p.B = (const float2*)x;
+  p.C = (float2*)z;
+  return S2C_LAUNCH(cgemm_grouped, cgemm_total_tiles(p), 256, cgemm_smem_bytes(), as_stream(st), p);
+}
+
 
 }  // extern "C"
 

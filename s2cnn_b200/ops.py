@@ -320,6 +320,27 @@ class Ops:
         return out.view(*lead, m, m, m)
 
     # -- host generators -----------------------------------------------------------------------
+    def so3_rotation_matrices(self, b, alpha, beta, gamma):
+        """Host: concatenated Wigner-D matrices [b(4b^2-1)/3, 2] of one rotation."""
+        import numpy as np
+        U = np.empty((so3_nspec(b), 2), dtype=np.float32)
+        self.lib.call("s2c_so3_rotation_matrices", b, float(alpha), float(beta), float(gamma),
+                      U.ctypes.data)
+        return U
+
+    def so3_rotate_spectrum(self, U, x, b, adjoint=False):
+        """x [nspec3, ..., 2] -> rotated spectrum of the same shape (adjoint: transposed map)."""
+        self._prep(U, x)
+        if x.shape[0] != so3_nspec(b) or x.shape[-1] != 2 or tuple(U.shape) != (so3_nspec(b), 2):
+            raise ValueError("so3_rotate_spectrum: bad shapes")
+        x = x.contiguous()
+        nbatch = _prod(tuple(x.shape[1:-1]))
+        out = torch.empty_like(x)
+        with self._ctx(x):
+            self.lib.call("s2c_so3_rotate_spectrum", U.data_ptr(), x.data_ptr(), out.data_ptr(), b,
+                          nbatch, int(adjoint), self._stream(x))
+        return out
+
     def so3_ft_matrix(self, b, grid):
         import numpy as np
         g = np.ascontiguousarray(np.asarray(grid, dtype=np.float64).reshape(len(grid), 3))

@@ -40,8 +40,28 @@ def save(name, **arrays):
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
 
 
+def rotation_cases():
+    """so3_rotation (s2cnn/soft/so3_rotation.py:11-48) with its gradient; own RNG so that
+    ``python tests/golden/make_golden.py rotation`` regenerates only these."""
+    from s2cnn import so3_rotation
+    from s2cnn.soft.so3_rotation import _setup_so3_rotation
+    g = torch.Generator().manual_seed(20240608)
+    with ref_import.in_scratch():
+        for b, nb, abc in ((4, (2, 3), (0.5, 1.0, 0.0)), (7, (2,), (2.1, 0.3, -1.2))):
+            x = torch.randn(*nb, 2 * b, 2 * b, 2 * b, generator=g).requires_grad_(True)
+            y = so3_rotation(x, *abc)
+            gy = torch.randn(*y.shape, generator=g)
+            y.backward(gy)
+            Us = _setup_so3_rotation(b, *abc, device_type="cpu", device_index=None)
+            U = torch.cat([u.reshape(-1, 2) for u in Us], 0)
+            save("so3_rotation_%d" % b, b=b, abc=np.array(abc), x=x, y=y, gy=gy, gx=x.grad, U=U)
+
+
 def main():
     ref = ref_import.load()
+    if sys.argv[1:] == ["rotation"]:
+        rotation_cases()
+        return
     from s2cnn.soft.so3_fft import so3_fft, so3_rfft, so3_ifft, so3_rifft
     from s2cnn.soft.s2_fft import s2_fft, s2_ifft
     import s2cnn
@@ -161,6 +181,7 @@ def main():
              so3_5_4_w=_setup_so3_fft(5, 4, True), so3_5_4_u=_setup_so3_fft(5, 4, False),
              so3_3_6_w=_setup_so3_fft(3, 6, True),
              s2_6_5_w=_setup_s2_fft(6, 5, True), s2_6_5_u=_setup_s2_fft(6, 5, False))
+    rotation_cases()
     print("golden fixtures written to", HERE)
 
 
