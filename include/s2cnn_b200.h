@@ -80,9 +80,14 @@ int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, i
  * "unsupported". */
 int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_out,
                       void* workspace, size_t workspace_bytes, void* stream);
-/* Test switch (no counterpart in the reference): non-zero routes small bandwidths through the
- * general three-pass kernels instead of the single-kernel path, so both can be checked. */
-void s2c_debug_force_general_path(int on);
+/* Test switches (no counterpart in the reference).  level 1 routes small bandwidths (2b <= 32)
+ * through the general kernels instead of the single-kernel path; level 2 additionally replaces the
+ * plane kernels of 2b = 64 / 128 (both row transforms of a (z, beta) plane in one kernel) by the
+ * three separate passes every other size uses; 0 restores the defaults. */
+void s2c_debug_force_general_path(int level);
+/* Plane kernels: 0 (default) = thread-block clusters of 8 beta planes exchanging through
+ * distributed shared memory; 1 = independent blocks, no clusters. */
+void s2c_debug_plane_width(int planes);
 /* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].
  * Replaces so3_fft, s2cnn/soft/so3_fft.py:12-61. */
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,

@@ -61,6 +61,9 @@ typedef cudaStream_t stream_t;
 struct Ctx {
   int tid, nthr, bid, nblk;
   __device__ __forceinline__ void sync() const { __syncthreads(); }
+  // barrier among the 32 threads of a warp (every warp of the block must call it equally often:
+  // the emulation build implements it as a block barrier)
+  __device__ __forceinline__ void sync_warp() const { __syncwarp(); }
 };
 
 inline int cuda_check(cudaError_t e, const char* what) {
@@ -260,6 +263,7 @@ struct Ctx {
     EmuBlock* b = emu_cur();
     if (b->nthr > 1) swapcontext(&b->th[tid], &b->sched);
   }
+  void sync_warp() const { sync(); }
 };
 
 inline void emu_trampoline() {

@@ -11,6 +11,7 @@
 #include "tables.h"
 #include "fft_device.h"
 #include "so3_kernels.h"
+#include "so3_plane_kernels.h"
 #include "so3_fused_kernels.h"
 #include "wigner_tiled.h"
 #include "cgemm_kernels.h"
@@ -19,7 +20,8 @@
 
 namespace s2c {
 thread_local long g_launch_count = 0;
-static bool g_force_general = false;  // test switch: route small bandwidths through the general path
+static int g_force_general = 0;   // test switch: 1 = no single-kernel path, 2 = also no plane kernels
+static int g_plane_width = 0;     // plane kernels: 0 = clusters of 8 planes exchanging V, 1 = no clusters
 
 #define S2C_TRY(expr)            \
   do {                           \
@@ -44,6 +46,29 @@ static size_t so3_ws_per_z(int N, int K) {
   return ((size_t)K * N * N + (size_t)K * (2 * K - 1) * N) * sizeof(float2);
 }
 static size_t s2_ws_per_z(int N, int K) { return (size_t)(2 * K - 1) * N * sizeof(float2); }
+
+static size_t so3_v_per_z(int N, int K) { return (size_t)K * (2 * K - 1) * N * sizeof(float2); }
+
+// Plane kernels (both row transforms of a (z, beta) plane in one kernel) for N = 64 and 128.
+static bool use_plane_kernels(int N) { return plane_supported(N) && g_force_general < 2; }
+static int launch_fwd_plane(int N, long zc, stream_t st, const FwdPlaneParams& f) {
+  const long grid = zc * N;
+  if (g_plane_width == 0) {
+    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 128, false, grid, st, f);
+    return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 64, false, grid, st, f);
+  }
+  if (N == 128) return S2C_LAUNCH_PLANE(so3_fwd_plane, 128, false, grid, st, f);
+  return S2C_LAUNCH_PLANE(so3_fwd_plane, 64, false, grid, st, f);
+}
+static int launch_inv_plane(int N, long zc, stream_t st, const InvPlaneParams& f) {
+  const long grid = zc * N;
+  if (g_plane_width == 0) {
+    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 128, true, grid, st, f);
+    return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 64, true, grid, st, f);
+  }
+  if (N == 128) return S2C_LAUNCH_PLANE(so3_inv_plane, 128, true, grid, st, f);
+  return S2C_LAUNCH_PLANE(so3_inv_plane, 64, true, grid, st, f);
+}
 
 static int check_b(int b_in, int b_out) {
   if (b_in < 1 || b_out < 1) return fail(S2C_ERR_BAD_ARG, "bandwidths must be >= 1");
@@ -85,10 +110,19 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
                                        std::to_string(per_z) + " bytes needed)");
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
+  const bool plane = use_plane_kernels(N);
+  if (plane) chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / so3_v_per_z(N, K));
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     float2* u = (float2*)ws;
-    float2* v = u + (size_t)zc * K * N * N;
+    float2* v = plane ? u : u + (size_t)zc * K * N * N;
+    if (plane) {
+      FwdPlaneParams f;
+      f.x = x + (size_t)z0 * N * N * N * in_stride;
+      f.in_stride = in_stride; f.in_off = in_off;
+      f.v = v; f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
+      S2C_TRY(launch_fwd_plane(N, zc, st, f));
+    } else {
     FwdGammaParams g;
     g.x = x + (size_t)z0 * N * N * N * in_stride;
     g.in_stride = in_stride;
@@ -106,6 +140,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     a.nrows = zc * K * N;
     a.fft = fft;
     S2C_TRY(S2C_LAUNCH(so3_fwd_alpha, (a.nrows + G - 1) / G, kThreads, fft_smem, st, a));
+    }
     FwdWignerParams w;
     w.v = v;
     w.out = out + z0;
@@ -182,10 +217,12 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
                                        std::to_string(per_z) + " bytes needed)");
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
+  const bool plane = use_plane_kernels(N);
+  if (plane) chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / so3_v_per_z(N, K));
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
-    float2* t = (float2*)ws;                       // [z][K][N][N]
-    float2* s = t + (size_t)zc * K * N * N;        // [K][2K-1][z][N]
+    float2* t = (float2*)ws;                                   // [z][K][N][N]
+    float2* s = plane ? t : t + (size_t)zc * K * N * N;        // [K][2K-1][z][N]
     InvWignerParams w;
     w.x = x + z0;
     w.x_zstride = nbatch;
@@ -203,6 +240,16 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     } else {
       const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
       S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
+    }
+    if (plane) {
+      InvPlaneParams f;
+      f.s = s;
+      f.out = out + (size_t)z0 * N * N * N * out_stride;
+      f.out_stride = out_stride; f.out_off = out_off;
+      f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1; f.z0 = z0;
+      f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
+      S2C_TRY(launch_inv_plane(N, zc, st, f));
+      continue;
     }
     InvAlphaParams a;
     a.s = s;
@@ -422,7 +469,8 @@ int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_o
                       as_stream(stream), true);
 }
 
-void s2c_debug_force_general_path(int on) { g_force_general = on != 0; }
+void s2c_debug_force_general_path(int level) { g_force_general = level < 0 ? 0 : level; }
+void s2c_debug_plane_width(int planes) { g_plane_width = planes == 1 ? 1 : 0; }
 
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                 void* ws, size_t ws_bytes, void* stream) {
