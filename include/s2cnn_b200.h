@@ -85,7 +85,7 @@ int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_o
  * plane kernels of 2b = 64 / 128 (both row transforms of a (z, beta) plane in one kernel) by the
  * three separate passes every other size uses; 0 restores the defaults. */
 void s2c_debug_force_general_path(int level);
-/* Plane kernels: 0 (default) = thread-block clusters of 8 beta planes exchanging through
+/* Plane kernels: 0 (default) = thread-block clusters of 4 beta planes exchanging through
  * distributed shared memory; 1 = independent blocks, no clusters. */
 void s2c_debug_plane_width(int planes);
 /* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].

@@ -21,7 +21,7 @@
 namespace s2c {
 thread_local long g_launch_count = 0;
 static int g_force_general = 0;   // test switch: 1 = no single-kernel path, 2 = also no plane kernels
-static int g_plane_width = 0;     // plane kernels: 0 = clusters of 8 planes exchanging V, 1 = no clusters
+static int g_plane_width = 0;     // plane kernels: 0 = clusters of planes exchanging V, 1 = no clusters
 
 #define S2C_TRY(expr)            \
   do {                           \
@@ -54,20 +54,20 @@ static bool use_plane_kernels(int N) { return plane_supported(N) && g_force_gene
 static int launch_fwd_plane(int N, long zc, stream_t st, const FwdPlaneParams& f) {
   const long grid = zc * N;
   if (g_plane_width == 0) {
-    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 128, false, grid, st, f);
-    return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 64, false, grid, st, f);
+    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 128, grid, st, f);
+    return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 64, grid, st, f);
   }
-  if (N == 128) return S2C_LAUNCH_PLANE(so3_fwd_plane, 128, false, grid, st, f);
-  return S2C_LAUNCH_PLANE(so3_fwd_plane, 64, false, grid, st, f);
+  if (N == 128) return S2C_LAUNCH_PLANE(so3_fwd_plane, 128, grid, st, f);
+  return S2C_LAUNCH_PLANE(so3_fwd_plane, 64, grid, st, f);
 }
 static int launch_inv_plane(int N, long zc, stream_t st, const InvPlaneParams& f) {
   const long grid = zc * N;
   if (g_plane_width == 0) {
-    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 128, true, grid, st, f);
-    return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 64, true, grid, st, f);
+    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 128, grid, st, f);
+    return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 64, grid, st, f);
   }
-  if (N == 128) return S2C_LAUNCH_PLANE(so3_inv_plane, 128, true, grid, st, f);
-  return S2C_LAUNCH_PLANE(so3_inv_plane, 64, true, grid, st, f);
+  if (N == 128) return S2C_LAUNCH_PLANE(so3_inv_plane, 128, grid, st, f);
+  return S2C_LAUNCH_PLANE(so3_inv_plane, 64, grid, st, f);
 }
 
 static int check_b(int b_in, int b_out) {

@@ -25,11 +25,15 @@
 // V is beta-innermost (the Wigner contraction runs over beta), so a block that owns one plane
 // touches V in isolated 8-byte pieces - measured on a B200 at b = 64 that alone makes the kernel
 // slower than the two passes it replaces.  The CL = true variants therefore run as thread-block
-// clusters of 8 consecutive beta planes of one signal and exchange through distributed shared
-// memory: each warp parks its four columns of V in its own transpose buffer, and after a cluster
-// barrier block r moves the r-th eighth of the entries for all 8 planes - 64 contiguous bytes per
-// entry - between the blocks' shared memories and global memory.  The CL = false variants touch V
-// directly; the host-emulation build and the tests use them as a second implementation.
+// clusters of 4 consecutive beta planes of one signal and exchange through distributed shared
+// memory: each warp parks its columns of V in its own transpose buffer, and after a cluster
+// barrier block r moves the r-th quarter of the entries for all 4 planes - 32 contiguous bytes per
+// entry, neighbouring lanes on neighbouring 16-byte pieces - between the blocks' shared memories
+// and global memory.  (Measured at b = 64, batch 64: 8 B pieces 1.2 ms, clusters of 4 0.52 ms,
+// clusters of 8 0.58 ms; of the 0.52 ms about 0.20 is arithmetic and shared-memory traffic, 0.14
+// the stores of V, 0.11 the remote shared-memory reads, 0.07 the input loads, 0.05 the barriers.)
+// The CL = false variants touch V directly; the host-emulation build and the tests use them as a
+// second implementation.
 #pragma once
 
 #include "backend.h"
@@ -42,9 +46,8 @@
 
 namespace s2c {
 
-constexpr int kPlaneCluster = 8;   // blocks (beta planes) per cluster of the CL variants
-constexpr int kPlaneWarps = 8;     // warps per block
-constexpr int kPlaneThreads = 32 * kPlaneWarps;
+constexpr int kPlaneCluster = 4;   // blocks (beta planes) per cluster of the CL variants (8 measured slower)
+constexpr int kPlaneRW = 4;        // rows (or columns) a warp transforms at a time: 4 (8 warps) or 2 (16 warps, measured slower)
 
 #ifndef S2C_EMUL
 __device__ __forceinline__ unsigned plane_cluster_rank() {
@@ -86,14 +89,25 @@ S2C_HD constexpr int plane_rb(int N) { return N / 8; }              // N = 8 * R
 S2C_HD constexpr int plane_ldb(int N) { return N + 1; }             // odd row stride of the plane
 // row stride of a transpose buffer whose first step has radix R1: >= N + R1 - 1 and = 8 mod 16
 S2C_HD constexpr int plane_ldt(int N, int R1) { return (N + R1 - 1 + 7) / 16 * 16 + 8; }
-// complex numbers per warp-private buffer (four rows)
-S2C_HD constexpr int plane_wt(int N, bool inverse) { return 4 * plane_ldt(N, inverse ? plane_rb(N) : 8); }
-inline size_t plane_smem_bytes(int N, bool inverse) {
-  return ((size_t)N + (size_t)(N / 2) * plane_ldb(N) + (size_t)kPlaneWarps * plane_wt(N, inverse)) *
+// RW rows per warp at a time: 32 / RW warps per block cover 32 columns (or row pairs) per pass
+S2C_HD constexpr int plane_warps(int RW) { return 32 / RW; }
+S2C_HD constexpr int plane_threads(int RW) { return 32 * plane_warps(RW); }
+// complex numbers per warp-private buffer (RW rows)
+S2C_HD constexpr int plane_wt(int N, int RW) { return RW * plane_ldt(N, 8); }
+inline size_t plane_smem_bytes(int N, int RW) {
+  return ((size_t)N + (size_t)(N / 2) * plane_ldb(N) + (size_t)plane_warps(RW) * plane_wt(N, RW)) *
          sizeof(float2);
 }
-// rows {base, base+8, base+1, base+9} of row group g (16 groups cover 64 rows)
-S2C_HD constexpr int plane_row(int g, int tl) { return 16 * (g / 4) + 2 * (g % 4) + (tl & 1) * 8 + (tl >> 1); }
+// row tl of row group g: rows of one group differ by 8 (and 1), e.g. {t, t+8, t+1, t+9} for RW = 4
+S2C_HD constexpr int plane_row(int RW, int g, int tl) {
+  return RW == 4 ? 16 * (g / 4) + 2 * (g % 4) + (tl & 1) * 8 + (tl >> 1)
+                 : 16 * (g / 8) + (g % 8) + 8 * tl;
+}
+// column chunk of 32: warp w owns columns first + 8 i, i < RW
+S2C_HD constexpr int plane_col0(int RW, int warp) { return (warp % 8) + 8 * RW * (warp / 8); }
+// ... and column nl of the chunk lives in this warp / this row of the warp's buffer
+S2C_HD constexpr int plane_col_warp(int RW, int nl) { return (nl % 8) + 8 * (nl / (8 * RW)); }
+S2C_HD constexpr int plane_col_row(int RW, int nl) { return (nl / 8) % RW; }
 
 // step 1 output: frequency pc of the R1-point transform, times W_N^(j pc), to dst[pc * (R2 + 1)]
 template <int R1, int R2, int DIR>
@@ -106,12 +120,13 @@ S2C_D void plane_put_step1(float2 (&v)[R1], float2* dst, int j, const float2* tw
   });
 }
 
-template <int N, bool CL>
+template <int N, bool CL, int RW>
 struct so3_fwd_plane_impl {
   static S2C_D void run(const Ctx& ctx, const FwdPlaneParams& p, unsigned char* smem) {
     constexpr int RB = plane_rb(N);                 // both transforms: radix 8 first, then RB
-    constexpr int LDB = plane_ldb(N), LDT = plane_ldt(N, 8), WT = plane_wt(N, false);
-    constexpr int NG = (N / 2) / (4 * kPlaneWarps);  // row groups per warp
+    constexpr int LDB = plane_ldb(N), LDT = plane_ldt(N, 8), WT = plane_wt(N, RW);
+    constexpr int NW = plane_warps(RW);
+    constexpr int NG = (N / 2) / 32;                 // row groups per warp
     float2* tw = reinterpret_cast<float2*>(smem);
     float2* B = tw + N;                               // packed plane C[t][f], [N/2][LDB]
     float2* tmp = B + (size_t)(N / 2) * LDB;          // [warps][WT]
@@ -126,11 +141,12 @@ struct so3_fwd_plane_impl {
     // ---- FFT over gamma of the packed row pairs (t, t + N/2) -----------------------------------
     const long plane0 = ((z * N + beta) * N) * (long)N;
     for (int gi = 0; gi < NG; ++gi) {
-      const int g = gi * kPlaneWarps + warp;
+      const int g = gi * NW + warp;
 #pragma unroll
-      for (int it0 = 0; it0 < 4 * RB; it0 += 32) {
+      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
         const int it = it0 + lane, tl = it / RB, j = it % RB;
-        const long e1 = plane0 + (long)plane_row(g, tl) * N + j;
+        if (RW * RB < 32 && it >= RW * RB) continue;
+        const long e1 = plane0 + (long)plane_row(RW, g, tl) * N + j;
         const long e2 = e1 + (long)(N / 2) * N;
         float2 v[8];
 #pragma unroll
@@ -142,14 +158,14 @@ struct so3_fwd_plane_impl {
         plane_put_step1<8, RB, -1>(v, wtmp + tl * LDT + j, j, tw);
       }
       ctx.sync_warp();
-      {
+      if (lane < RW * 8) {
         const int tl = lane / 8, pq = lane % 8;
         const float2* src = wtmp + tl * LDT + pq * (RB + 1);
         float2 u[RB];
 #pragma unroll
         for (int j = 0; j < RB; ++j) u[j] = src[j];
         fft_reg<RB, -1>(u, tw);
-        float2* dst = B + plane_row(g, tl) * LDB + pq;
+        float2* dst = B + plane_row(RW, g, tl) * LDB + pq;
         static_for<0, RB>([&](auto q_) {
           constexpr int q = decltype(q_)::value;
           dst[8 * q] = u[fft_reg_pos<RB>(q)];
@@ -162,11 +178,11 @@ struct so3_fwd_plane_impl {
     // ---- FFT over alpha of the kept columns, Hermitian split on load ----------------------------
     const int nchunks = (K + 31) / 32;
     for (int c = 0; c < nchunks; ++c) {
-      const int n0 = c * 32 + warp;                   // this warp's columns: n0 + 8 i, i < 4
+      const int n0 = c * 32 + plane_col0(RW, warp);   // this warp's columns: n0 + 8 i, i < RW
 #pragma unroll
-      for (int it0 = 0; it0 < 4 * RB; it0 += 32) {
+      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
         const int it = it0 + lane, i = it / RB, j = it % RB;
-        const int n = n0 + 8 * i;
+        const int n = (RW * RB < 32 && it >= RW * RB) ? K : n0 + 8 * i;
         if (n < K) {
           const int nc = n == 0 ? 0 : N - n;
           float2 v[8];
@@ -183,7 +199,7 @@ struct so3_fwd_plane_impl {
       }
       ctx.sync_warp();
       const int i = lane / 8, pq = lane % 8;
-      const int n = n0 + 8 * i;
+      const int n = lane < RW * 8 ? n0 + 8 * i : K;
       float2 u[RB];
       if (n < K) {
         const float2* src = wtmp + i * LDT + pq * (RB + 1);
@@ -192,7 +208,7 @@ struct so3_fwd_plane_impl {
         fft_reg<RB, -1>(u, tw);
       }
       if constexpr (CL) {
-        // the four transpose rows become the exchange rows xb[i][mi] of this warp's columns
+        // the transpose rows become the exchange rows xb[i][mi] of this warp's columns
         ctx.sync_warp();
         if (n < K) {
           static_for<0, RB>([&](auto q_) {
@@ -206,21 +222,22 @@ struct so3_fwd_plane_impl {
         {
           const unsigned rank = plane_cluster_rank();
           const int ncols = (K - c * 32) < 32 ? (K - c * 32) : 32;
-          const int total = ncols * nm;
-          const int per = (total + kPlaneCluster - 1) / kPlaneCluster;
-          for (int e0 = ctx.tid; e0 < per; e0 += ctx.nthr) {
-            const int e = (int)rank * per + e0;
-            if (e >= total) continue;
-            const int nl = e / nm, mi = e - nl * nm;   // column c*32 + nl lives in warp nl%8, row nl/8
-            float2* cell = tmp + (nl % 8) * WT + (nl / 8) * LDT + mi;
-            float2 val[kPlaneCluster];
-#pragma unroll
-            for (int r = 0; r < kPlaneCluster; ++r) val[r] = *plane_cluster_ptr(cell, r);
+          // item = (entry, pair of planes): neighbouring lanes write neighbouring 16-byte pieces, so a
+          // warp's store covers whole 32-byte sectors
+          constexpr int HP = kPlaneCluster / 2;
+          const int entries = ncols * nm;
+          const int per = (entries + kPlaneCluster - 1) / kPlaneCluster;   // entries per block
+          const int e_lo = (int)rank * per;
+          const int e_cnt = (entries - e_lo) < per ? (entries - e_lo) : per;
+          for (int it = ctx.tid; it < e_cnt * HP; it += ctx.nthr) {
+            const int e = e_lo + it / HP, h = it % HP;
+            const int nl = e / nm, mi = e - nl * nm;
+            float2* cell = tmp + plane_col_warp(RW, nl) * WT + plane_col_row(RW, nl) * LDT + mi;
+            const float2 v0 = *plane_cluster_ptr(cell, 2 * h);
+            const float2 v1 = *plane_cluster_ptr(cell, 2 * h + 1);
             float4* dst = reinterpret_cast<float4*>(
                 p.v + ((((long)(c * 32 + nl)) * nm + mi) * p.nbatch + z) * N + (beta - (int)rank));
-#pragma unroll
-            for (int r = 0; r < kPlaneCluster / 2; ++r)
-              dst[r] = make_float4(val[2 * r].x, val[2 * r].y, val[2 * r + 1].x, val[2 * r + 1].y);
+            dst[h] = make_float4(v0.x, v0.y, v1.x, v1.y);
           }
         }
         plane_cluster_sync();   // peers are done with this block's exchange rows
@@ -240,13 +257,14 @@ struct so3_fwd_plane_impl {
   }
 };
 
-template <int N, bool CL>
+template <int N, bool CL, int RW>
 struct so3_inv_plane_impl {
   static S2C_D void run(const Ctx& ctx, const InvPlaneParams& p, unsigned char* smem) {
-    constexpr int RB = plane_rb(N);   // alpha: radix 8 then RB; gamma: RB then 8 (RB lanes on consecutive samples)
-    constexpr int LDB = plane_ldb(N), LDA = plane_ldt(N, 8), LDG = plane_ldt(N, RB);
-    constexpr int WT = plane_wt(N, true);
-    constexpr int NG = (N / 2) / (4 * kPlaneWarps);
+    constexpr int RB = plane_rb(N);                 // both transforms: radix 8 first, then RB
+    constexpr int LDB = plane_ldb(N), LDA = plane_ldt(N, 8), LDG = plane_ldt(N, 8);
+    constexpr int WT = plane_wt(N, RW);
+    constexpr int NW = plane_warps(RW);
+    constexpr int NG = (N / 2) / 32;
     float2* tw = reinterpret_cast<float2*>(smem);
     float2* B = tw + N;
     float2* tmp = B + (size_t)(N / 2) * LDB;
@@ -268,9 +286,9 @@ struct so3_inv_plane_impl {
     // ---- inverse FFT over m -> alpha of the kept columns, packed into row pairs on store --------
     const int nchunks = (K + 31) / 32;
     for (int c = 0; c < nchunks; ++c) {
-      const int n0 = c * 32 + warp;                   // this warp's columns: n0 + 8 i, i < 4
+      const int n0 = c * 32 + plane_col0(RW, warp);   // this warp's columns: n0 + 8 i, i < RW
       if constexpr (CL) {
-        // bring the chunk's slice of V for the cluster's 8 planes in, 64 contiguous bytes per entry,
+        // bring the chunk's slice of V for the cluster's planes in, 8 contiguous bytes per plane and entry,
         // and deal it out to the exchange rows xb[i][mi] of the warps that own the columns
         plane_cluster_sync();   // every block runs, and is done with its buffers of the previous chunk
         const unsigned rank = plane_cluster_rank();
@@ -281,7 +299,7 @@ struct so3_inv_plane_impl {
           const int e = (int)rank * per + e0;
           if (e >= total) continue;
           const int nl = e / nm, mi = e - nl * nm;
-          float2* cell = tmp + (nl % 8) * WT + (nl / 8) * LDA + mi;
+          float2* cell = tmp + plane_col_warp(RW, nl) * WT + plane_col_row(RW, nl) * LDA + mi;
           const float4* src = reinterpret_cast<const float4*>(
               p.s + ((((long)(c * 32 + nl)) * nm + mi) * p.nbatch + z) * N + (beta - (int)rank));
           float4 val[kPlaneCluster / 2];
@@ -296,9 +314,9 @@ struct so3_inv_plane_impl {
         plane_cluster_sync();
       }
 #pragma unroll
-      for (int it0 = 0; it0 < 4 * RB; it0 += 32) {
+      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
         const int it = it0 + lane, i = it / RB, j = it % RB;
-        const int n = n0 + 8 * i;
+        const int n = (RW * RB < 32 && it >= RW * RB) ? K : n0 + 8 * i;
         float2 v[8];
         if (n < K) {
           const float2* scol = p.s + (((long)n * nm) * p.nbatch + z) * N + beta;
@@ -324,7 +342,7 @@ struct so3_inv_plane_impl {
       ctx.sync_warp();
       {
         const int i = lane / 8, pq = lane % 8;
-        const int n = n0 + 8 * i;
+        const int n = lane < RW * 8 ? n0 + 8 * i : K;
         if (n < K) {
           const float2* src = wtmp + i * LDA + pq * (RB + 1);
           float2 u[RB];
@@ -355,32 +373,33 @@ struct so3_inv_plane_impl {
     if (p.bias) add = p.bias[(p.z0 + z) % p.nfeat];
     const long plane0 = ((z * N + beta) * N) * (long)N;
     for (int gi = 0; gi < NG; ++gi) {
-      const int g = gi * kPlaneWarps + warp;
-      {
-        const int tl = lane / 8, j = lane % 8;
-        const float2* src = B + plane_row(g, tl) * LDB + j;
-        float2 v[RB];
+      const int g = gi * NW + warp;
 #pragma unroll
-        for (int k = 0; k < RB; ++k) v[k] = src[8 * k];
-        fft_reg<RB, +1>(v, tw);
-        plane_put_step1<RB, 8, +1>(v, wtmp + tl * LDG + j, j, tw);
+      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
+        const int it = it0 + lane, tl = it / RB, j = it % RB;
+        if (RW * RB < 32 && it >= RW * RB) continue;
+        const float2* src = B + plane_row(RW, g, tl) * LDB + j;
+        float2 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = src[RB * k];
+        fft_reg<8, +1>(v, tw);
+        plane_put_step1<8, RB, +1>(v, wtmp + tl * LDG + j, j, tw);
       }
       ctx.sync_warp();
+      if (lane < RW * 8) {
+        const int tl = lane / 8, pq = lane % 8;
+        const float2* src = wtmp + tl * LDG + pq * (RB + 1);
+        float2 u[RB];
 #pragma unroll
-      for (int it0 = 0; it0 < 4 * RB; it0 += 32) {
-        const int it = it0 + lane, tl = it / RB, pq = it % RB;
-        const float2* src = wtmp + tl * LDG + pq * 9;
-        float2 u[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) u[j] = src[j];
-        fft_reg<8, +1>(u, tw);
-        const long e1 = plane0 + (long)plane_row(g, tl) * N + pq;
+        for (int j = 0; j < RB; ++j) u[j] = src[j];
+        fft_reg<RB, +1>(u, tw);
+        const long e1 = plane0 + (long)plane_row(RW, g, tl) * N + pq;
         const long e2 = e1 + (long)(N / 2) * N;
-        static_for<0, 8>([&](auto q_) {
+        static_for<0, RB>([&](auto q_) {
           constexpr int q = decltype(q_)::value;
-          const float2 val = u[fft_reg_pos<8>(q)];
-          p.out[(e1 + RB * q) * p.out_stride + p.out_off] = val.x + add;
-          p.out[(e2 + RB * q) * p.out_stride + p.out_off] = val.y + add;
+          const float2 val = u[fft_reg_pos<RB>(q)];
+          p.out[(e1 + 8 * q) * p.out_stride + p.out_off] = val.x + add;
+          p.out[(e2 + 8 * q) * p.out_stride + p.out_off] = val.y + add;
         });
       }
       ctx.sync_warp();
@@ -390,44 +409,45 @@ struct so3_inv_plane_impl {
 
 #ifndef S2C_EMUL
 template <int N>
-__global__ void __launch_bounds__(kPlaneThreads, 2) so3_fwd_plane(const FwdPlaneParams p) {
+__global__ void __launch_bounds__(plane_threads(kPlaneRW), 2) so3_fwd_plane(const FwdPlaneParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
-  so3_fwd_plane_impl<N, false>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+  so3_fwd_plane_impl<N, false, kPlaneRW>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
 template <int N>
-__global__ void __launch_bounds__(kPlaneThreads, 2) so3_inv_plane(const InvPlaneParams p) {
+__global__ void __launch_bounds__(plane_threads(kPlaneRW), 2) so3_inv_plane(const InvPlaneParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
-  so3_inv_plane_impl<N, false>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+  so3_inv_plane_impl<N, false, kPlaneRW>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
-// cluster variants: 8 consecutive blocks = 8 consecutive beta planes of one signal (N % 8 == 0)
+// cluster variants: consecutive blocks = consecutive beta planes of one signal (N % cluster == 0)
 template <int N>
-__global__ void __cluster_dims__(kPlaneCluster, 1, 1) __launch_bounds__(kPlaneThreads, 2)
+__global__ void __cluster_dims__(kPlaneCluster, 1, 1) __launch_bounds__(plane_threads(kPlaneRW), 2)
 so3_fwd_plane_cl(const FwdPlaneParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
-  so3_fwd_plane_impl<N, true>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+  so3_fwd_plane_impl<N, true, kPlaneRW>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
 template <int N>
-__global__ void __cluster_dims__(kPlaneCluster, 1, 1) __launch_bounds__(kPlaneThreads, 2)
+__global__ void __cluster_dims__(kPlaneCluster, 1, 1) __launch_bounds__(plane_threads(kPlaneRW), 2)
 so3_inv_plane_cl(const InvPlaneParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
-  so3_inv_plane_impl<N, true>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+  so3_inv_plane_impl<N, true, kPlaneRW>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
-#define S2C_LAUNCH_PLANE(name, N, inverse, grid, stream, params)                              \
-  s2c::launch_impl(name<N>, #name, (long)(grid), s2c::kPlaneThreads,                          \
-                   s2c::plane_smem_bytes(N, inverse), stream, params)
-#define S2C_LAUNCH_PLANE_CL(name, N, inverse, grid, stream, params)                           \
-  s2c::launch_impl(name##_cl<N>, #name "_cl", (long)(grid), s2c::kPlaneThreads,               \
-                   s2c::plane_smem_bytes(N, inverse), stream, params)
+#define S2C_LAUNCH_PLANE(name, N, grid, stream, params)                                       \
+  s2c::launch_impl(name<N>, #name, (long)(grid), s2c::plane_threads(s2c::kPlaneRW),           \
+                   s2c::plane_smem_bytes(N, s2c::kPlaneRW), stream, params)
+#define S2C_LAUNCH_PLANE_CL(name, N, grid, stream, params)                                    \
+  s2c::launch_impl(name##_cl<N>, #name "_cl", (long)(grid), s2c::plane_threads(s2c::kPlaneRW),\
+                   s2c::plane_smem_bytes(N, s2c::kPlaneRW), stream, params)
 #else
-#define S2C_LAUNCH_PLANE(name, N, inverse, grid, stream, params)                              \
-  s2c::emu_launch<name##_impl<N, false>>(#name, (long)(grid), s2c::kPlaneThreads,             \
-                                         s2c::plane_smem_bytes(N, inverse), params)
-#define S2C_LAUNCH_PLANE_CL(name, N, inverse, grid, stream, params)                           \
-  S2C_LAUNCH_PLANE(name, N, inverse, grid, stream, params)
+#define S2C_LAUNCH_PLANE(name, N, grid, stream, params)                                       \
+  s2c::emu_launch<name##_impl<N, false, s2c::kPlaneRW>>(                                      \
+      #name, (long)(grid), s2c::plane_threads(s2c::kPlaneRW),                                 \
+      s2c::plane_smem_bytes(N, s2c::kPlaneRW), params)
+#define S2C_LAUNCH_PLANE_CL(name, N, grid, stream, params)                                    \
+  S2C_LAUNCH_PLANE(name, N, grid, stream, params)
 #endif
 
 }  // namespace s2c
