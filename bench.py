@@ -352,6 +352,37 @@ def so3_fft_b64(device, hbm_gbs):
     return res
 
 
+def so3_mm_tensor(device, bf16_tf):
+    """The spectral product of the widest layer BASELINE's deep model holds (SO3Conv 100 -> 100 at
+    b_out = 10, batch 32): time of so3_mm on the tcgen05 path, algorithmic flops (8 per complex
+    multiply-add) and the TF32 flops actually issued (three TF32 products per FP32 product),
+    against half of the measured bf16 GEMM peak (TF32 runs at half the bf16 rate)."""
+    from s2cnn_b200 import so3_mm
+    nl, nb, fi, fo = 10, 32, 100, 100
+    x = torch.randn(n3(nl), nb, fi, 2, device=device)
+    y = torch.randn(n3(nl), fi, fo, 2, device=device)
+    for _ in range(3):
+        so3_mm(x, y)
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(10):
+        a = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        a.record()
+        so3_mm(x, y)
+        e.record()
+        e.synchronize()
+        ts.append(a.elapsed_time(e))
+    ms = float(np.median(ts))
+    flops = 8.0 * sum((2 * l + 1) ** 3 for l in range(nl)) * nb * fi * fo
+    issued = 3.0 * flops / (ms * 1e-3) / 1e12
+    peak = bf16_tf / 2.0
+    return {"workload": "so3_mm nl=10 batch=32 f_in=100 f_out=100 (operands L2-resident)",
+            "ms": ms, "algorithmic_TFLOPs": flops / (ms * 1e-3) / 1e12,
+            "issued_tf32_TFLOPs": issued, "peak_tf32_TFLOPs": peak,
+            "peak_source": "half of the measured bf16 GEMM peak", "frac": issued / peak}
+
+
 def run_ours(args):
     world, rank, local = dist_setup(args.gpus)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback exists)"
@@ -503,6 +534,7 @@ def run_ours(args):
                                     "sample": "full batch of %d, best of 3 (%.2f s each)" % (B, best)}
         if world == 1 and not args.skip_fft64:
             line["so3_fft_b64"] = so3_fft_b64(device, hbm_gbs)
+            line["so3_mm_tensor"] = so3_mm_tensor(device, bf16_tf)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

@@ -150,7 +150,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     w.ZT = (int)std::min<long>(32, zc);
     w.nzt = (int)((zc + w.ZT - 1) / w.ZT);
     w.mode = mode;
-    if (N % 4 == 0 && fwd_wigner_t_smem(N, b_out) <= (size_t)dev_smem_limit() - 1024) {
+    if (N % (4 * kWigHalves) == 0 && fwd_wigner_t_smem(N, b_out) <= (size_t)dev_smem_limit() - 1024) {
       w.ZT = kWigZT;
       w.nzt = (int)((zc + kWigZT - 1) / kWigZT);
       S2C_TRY(S2C_LAUNCH(so3_fwd_wigner_t, (long)pan.npairs * w.nzt, kThreads,

@@ -8,6 +8,7 @@ within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hun
     inv10   so3_rifft, b = 10, 5120 signals          (kernel so3_inv_fused<20>)
     fwd10   so3_rfft,  b = 10 -> 6, 5120 signals     (kernel so3_fwd_fused<20>)
     mm      so3_mm, nl = 6, batch 256, 20 -> 40      (kernel so3_mm_tc_kernel)
+    mm_c4   so3_mm, nl = 10, batch 32, 100 -> 100    (kernel so3_mm_tc_kernel at a GEMM-sized case)
     fft64   so3_rfft + so3_rifft, b = 64, 8 signals  (general-path kernels)
 """
 import sys
@@ -32,6 +33,11 @@ def main(which):
     elif which == "mm":
         x = torch.randn(so3_nspec(6), 256, 20, 2, device=dev)
         y = torch.randn(so3_nspec(6), 20, 40, 2, device=dev)
+        for _ in range(3):
+            ops.so3_mm(x, y)
+    elif which == "mm_c4":
+        x = torch.randn(so3_nspec(10), 32, 100, 2, device=dev)
+        y = torch.randn(so3_nspec(10), 100, 100, 2, device=dev)
         for _ in range(3):
             ops.so3_mm(x, y)
     elif which == "fft64":
