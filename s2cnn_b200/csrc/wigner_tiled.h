@@ -28,7 +28,7 @@ inline size_t fwd_wigner_t_smem(int N, int nl) {
 // (0.40 ms) beats two (0.45 ms), so it is 1.  Panel rows and batch rows are staged exactly as they lie in memory (16-byte copies, no transposition): the
 // beta loop runs four samples at a time, a thread reads W[l][beta..beta+3] for its four degrees
 // (the whole warp shares the address: broadcast) and V[z][beta..beta+3] for its two batch elements
-// z = tz and tz + 32 (row stride N + 2 complex numbers, so the 8 lanes of a 16-byte access phase
+// z = tz and tz + ceil(zc/2) (row stride N + 2 complex numbers, so the 8 lanes of a 16-byte access phase
 // hit 8 different bank groups).
 S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
   const int N = p.N, NH = N / kWigHalves;
@@ -41,7 +41,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
   if (L <= 0) return;
   const int z0 = zt * kWigZT;
   const int zc = (p.nbatch - z0) < kWigZT ? (p.nbatch - z0) : kWigZT;
-  const int LDW = NH + 4, LDV = NH + 2, ZH = kWigZT / 2;
+  const int LDW = NH + 4, LDV = NH + 2, ZH = (zc + 1) / 2;   // a thread's batch elements: tz, tz + ZH
   float* Ws = reinterpret_cast<float*>(smem);                                        // [nl up to 4][LDW]
   float2* Vs = reinterpret_cast<float2*>(Ws + (size_t)((p.nl + 3) / 4 * 4) * LDW);    // [kWigZT][LDV]
   const int LT = (L + 3) / 4;
@@ -51,7 +51,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
   // 4 x 2 tiles (degrees x batch elements), or 4 x 1 when the pair has few degrees so that more
   // threads share the beta loop; at most two tiles per thread either way (LT <= 16, 256 threads)
   const bool narrow = LT * ZH < ctx.nthr;
-  const int ntiles = narrow ? LT * kWigZT : LT * ZH;
+  const int ntiles = narrow ? LT * zc : LT * ZH;
   float ar[2][4][2], ai[2][4][2];
 #pragma unroll
   for (int t = 0; t < 2; ++t)
@@ -84,7 +84,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
       }
     }
     {
-      const int n2 = NH / 2, total = kWigZT * n2;                     // rows past zc are zero
+      const int n2 = NH / 2, total = 2 * ZH * n2;                     // a row past zc is zero
       for (int base = ctx.tid; base < total; base += 4 * ctx.nthr) {
         float4 v[4];
 #pragma unroll
@@ -112,7 +112,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
       const int tile = ctx.tid + t * ctx.nthr;
       if (tile >= ntiles) continue;
       if (narrow) {
-        const int tl = tile / kWigZT, zz = tile - tl * kWigZT;
+        const int tl = tile / zc, zz = tile - tl * zc;
         const float* wp = Ws + 4 * tl * LDW;
         const float2* vp = Vs + zz * LDV;
         for (int bt = 0; bt < NH; bt += 4) {
@@ -138,7 +138,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
           for (int i = 0; i < 4; ++i) w4[i] = *reinterpret_cast<const float4*>(wp + i * LDW + bt);
           const float4 a0 = *reinterpret_cast<const float4*>(v0 + bt);       // beta, beta+1 of z = tz
           const float4 b0 = *reinterpret_cast<const float4*>(v0 + bt + 2);   // beta+2, beta+3
-          const float4 a1 = *reinterpret_cast<const float4*>(v1 + bt);       // z = tz + 32
+          const float4 a1 = *reinterpret_cast<const float4*>(v1 + bt);       // z = tz + ZH
           const float4 b1 = *reinterpret_cast<const float4*>(v1 + bt + 2);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -180,7 +180,7 @@ S2C_KERNEL(so3_fwd_wigner_t, FwdWignerParams) {
     const int tile = ctx.tid + t * ctx.nthr;
     if (tile >= ntiles) continue;
     if (narrow) {
-      const int tl = tile / kWigZT, zz = tile - tl * kWigZT;
+      const int tl = tile / zc, zz = tile - tl * zc;
 #pragma unroll
       for (int i = 0; i < 4; ++i) emit(4 * tl + i, zz, ar[t][i][0], ai[t][i][0]);
     } else {

@@ -9,7 +9,8 @@ within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hun
     fwd10   so3_rfft,  b = 10 -> 6, 5120 signals     (kernel so3_fwd_fused<20>)
     mm      so3_mm, nl = 6, batch 256, 20 -> 40      (kernel so3_mm_tc_kernel)
     mm_c4   so3_mm, nl = 10, batch 32, 100 -> 100    (kernel so3_mm_tc_kernel at a GEMM-sized case)
-    fft64   so3_rfft + so3_rifft, b = 64, 8 signals  (general-path kernels)
+    fft64   so3_rfft + so3_rifft, b = 64, 8 signals  (plane kernels + Wigner contraction)
+    fft64_three_pass   the same through the three separate passes (the path 2b = 256 takes)
 """
 import sys
 
@@ -40,10 +41,12 @@ def main(which):
         y = torch.randn(so3_nspec(10), 100, 100, 2, device=dev)
         for _ in range(3):
             ops.so3_mm(x, y)
-    elif which == "fft64":
+    elif which in ("fft64", "fft64_three_pass"):
         x = torch.randn(8, 128, 128, 128, device=dev)
+        ops.lib.s2c_debug_force_general_path(2 if which == "fft64_three_pass" else 0)
         for _ in range(2):
             ops.so3_rifft(ops.so3_rfft(x))
+        ops.lib.s2c_debug_force_general_path(0)
     else:
         raise SystemExit(__doc__)
     torch.cuda.synchronize()
