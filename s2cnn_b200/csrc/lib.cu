@@ -625,23 +625,40 @@ int s2c_s2_ifft(const float* x, float* out, int out_is_real, long nbatch, int b_
 static __device__ int g_tc_err_flag;
 #endif
 
+#ifndef S2C_EMUL
+// so3_mm or one of its gradients on the tensor cores; `handled` tells whether the shape qualified.
+static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, int nl, int nb, int fi,
+                            int fo, stream_t st, bool* handled) {
+  *handled = !g_force_general && so3_mm_tc_supported(op, nb, fi, fo);
+  if (!*handled) return S2C_OK;
+  MmTcParams p;
+  p.a = a; p.b = b; p.c = c;
+  p.nl = nl; p.nb = nb; p.fi = fi; p.fo = fo;
+  p.run = 2 * (op == kTcFwd ? fi : op == kTcGradX ? fo : nb);
+  if (p.run <= kTcKMax) { p.kblk = (p.run + 7) / 8 * 8; p.nblk = 1; }
+  else { p.kblk = kTcKMax; p.nblk = (p.run + kTcKMax - 1) / kTcKMax; }
+  void* flag = nullptr;
+  S2C_TRY(cuda_check(cudaGetSymbolAddress(&flag, g_tc_err_flag), "tensor-core status flag"));
+  p.err = (int*)flag;
+  const long tiles = so3_mm_tc_tiles(op, nl, nb, fi, fo);
+  const bool flush = (long)(2 * nl - 1) * p.nblk > kTcFlushBlocks;   // longest K loop of any degree
+#define S2C_TC_LAUNCH(OP, NAME)                                                                   \
+  (flush ? launch_impl(so3_mm_tc_kernel<OP, true>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p)   \
+         : launch_impl(so3_mm_tc_kernel<OP, false>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p))
+  if (op == kTcFwd) return S2C_TC_LAUNCH(kTcFwd, "so3_mm_tc_kernel");
+  if (op == kTcGradX) return S2C_TC_LAUNCH(kTcGradX, "so3_mm_tc_gradx");
+  return S2C_TC_LAUNCH(kTcGradY, "so3_mm_tc_grady");
+#undef S2C_TC_LAUNCH
+}
+#endif
+
 int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, int fo, void* st) {
   if (!x || !y || !z) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm: null pointer");
   if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
 #ifndef S2C_EMUL
-  if (!g_force_general && so3_mm_tc_supported(nl, nb, fi, fo)) {
-    MmTcParams p;
-    p.x = x; p.y = y; p.z = z;
-    p.nl = nl; p.nb = nb; p.fi = fi; p.fo = fo;
-    const int fi2 = 2 * fi;
-    if (fi2 <= kTcKMax) { p.kblk = (fi2 + 7) / 8 * 8; p.nblk = 1; }
-    else { p.kblk = kTcKMax; p.nblk = (fi2 + kTcKMax - 1) / kTcKMax; }
-    void* flag = nullptr;
-    S2C_TRY(cuda_check(cudaGetSymbolAddress(&flag, g_tc_err_flag), "tensor-core status flag"));
-    p.err = (int*)flag;
-    return launch_impl(so3_mm_tc_kernel, "so3_mm_tc_kernel", so3_mm_tc_tiles(nl, nb, fo),
-                       kTcThreads, kTcSmemBytes, as_stream(st), p);
-  }
+  bool handled = false;
+  S2C_TRY(so3_mm_tc_launch(kTcFwd, x, y, z, nl, nb, fi, fo, as_stream(st), &handled));
+  if (handled) return S2C_OK;
 #endif
   return mm_dispatch(true, kMmFwd, x, y, z, nl, nb, fi, fo, as_stream(st));
 }
@@ -658,11 +675,23 @@ int s2c_so3_mm_tc_status(void) {
 int s2c_so3_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nb, int fi, int fo,
                      void* st) {
   if (!gz || !y || !gx) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm_gradx: null pointer");
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+#ifndef S2C_EMUL
+  bool handled = false;
+  S2C_TRY(so3_mm_tc_launch(kTcGradX, gz, y, gx, nl, nb, fi, fo, as_stream(st), &handled));
+  if (handled) return S2C_OK;
+#endif
   return mm_dispatch(true, kMmGradX, gz, y, gx, nl, nb, fi, fo, as_stream(st));
 }
 int s2c_so3_mm_grady(const float* gz, const float* x, float* gy, int nl, int nb, int fi, int fo,
                      void* st) {
   if (!gz || !x || !gy) return fail(S2C_ERR_BAD_ARG, "s2c_so3_mm_grady: null pointer");
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+#ifndef S2C_EMUL
+  bool handled = false;
+  S2C_TRY(so3_mm_tc_launch(kTcGradY, x, gz, gy, nl, nb, fi, fo, as_stream(st), &handled));
+  if (handled) return S2C_OK;
+#endif
   return mm_dispatch(true, kMmGradY, x, gz, gy, nl, nb, fi, fo, as_stream(st));
 }
 int s2c_s2_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, int fo, void* st) {

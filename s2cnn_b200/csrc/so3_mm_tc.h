@@ -1,4 +1,5 @@
-// so3_mm forward on the 5th-generation tensor cores (tcgen05.mma, accumulator in TMEM), 3xTF32.
+// so3_mm and its two gradients on the 5th-generation tensor cores (tcgen05.mma, accumulator in
+// TMEM), 3xTF32.
 //
 //   z[l,m,n,i,j] = sum_{p,k} x[l,m,p,i,k] conj(y[l,n,p,k,j])            (s2cnn/so3_mm.py:8-93)
 //
@@ -8,19 +9,24 @@
 // C' is the z tensor written as plain floats, and B' is built from y while staging:
 //   B'[(k,0),(j,0)] =  yr   B'[(k,1),(j,0)] = yi      (real part of x * conj(y))
 //   B'[(k,0),(j,1)] = -yi   B'[(k,1),(j,1)] = yr      (imaginary part)
-// so the complex product costs 8 real flops per complex MAC, the algorithmic count.
+// so the complex product costs 8 real flops per complex MAC, the algorithmic count.  The two
+// gradient products (s2cnn/so3_mm.py:95-122 and the backward kernels :125-261) have the same
+// shape with other row / column / contraction roles; the kernel is instantiated per product.
 //
 // Precision: TF32 has 10 mantissa bits, not enough for the 1e-4 bar.  Every operand is split in
-// float32 into hi = v truncated to TF32 and lo = v - hi and three MMAs (hi*hi, lo*hi, hi*lo) accumulate into
-// the same float32 TMEM accumulator, which restores float32-level accuracy.
+// float32 into hi = v truncated to TF32 and lo = v - hi and three MMAs (hi*hi, lo*hi, hi*lo)
+// accumulate into the same float32 TMEM accumulator.  The tensor core's own accumulation
+// truncates, which shows after thousands of K steps (grad y contracts over (2l+1) * batch); every
+// kTcFlushBlocks K blocks the partial sum is therefore moved out of the MMA accumulator and added
+// in FP32 by the threads into a second TMEM region.
 //
-// Tiling: one CTA per (l, 128-row tile, 128-column tile); the K loop walks the blocks (p, slice of
-// the 2*f_in floats).  Operands are staged by all 256 threads into shared memory in the canonical
-// K-major, no-swizzle UMMA layout (8 rows x 16 bytes core matrices), double buffered; one elected
-// thread issues tcgen05.mma and commits to an mbarrier that releases the stage.  The epilogue reads
-// the accumulator with tcgen05.ld (32 lanes x 32 columns per warp and instruction) and stores z
-// directly in its interleaved layout.  Every mbarrier wait is bounded; on a time-out the kernel
-// raises an error flag, frees its TMEM columns and returns.
+// Tiling: one CTA per (l, 128-row tile, 128-column tile); the K loop walks the blocks (outer
+// contraction index, slice of its run of floats).  Operands are staged by all 512 threads into
+// shared memory in the canonical K-major, no-swizzle UMMA layout (8 rows x 16 bytes core matrices),
+// double buffered; one elected thread issues tcgen05.mma and commits to an mbarrier that releases
+// the stage.  The epilogue reads the accumulator with tcgen05.ld (32 lanes x 32 columns per warp
+// and instruction) and stores the result directly in its interleaved layout.  Every mbarrier wait
+// is bounded; on a time-out the kernel raises an error flag, frees its TMEM columns and returns.
 #pragma once
 
 #ifndef S2C_EMUL
@@ -32,15 +38,40 @@
 
 namespace s2c {
 
+// The same kernel runs the forward product and its two gradients; they differ in how the rows
+// of the two operands are addressed and in the sign pattern that turns complex into real
+// arithmetic (the op code selects both):
+//   kTcFwd    z[l,m,n,i,j]  = sum_{p,k} x[l,m,p,i,k] conj(y[l,n,p,k,j])     a = x,  b = y,  c = z
+//   kTcGradX  gx[l,m,p,i,k] = sum_{n,j} gz[l,m,n,i,j] y[l,n,p,k,j]          a = gz, b = y,  c = gx
+//   kTcGradY  gy[l,n,p,k,j] = sum_{m,i} conj(gz[l,m,n,i,j]) x[l,m,p,i,k]    a = x,  b = gz, c = gy
+// (s2cnn/so3_mm.py:8-122).  An output row is (outer, inner) = (m, i) - or (p, k) for kTcGradY - and
+// an output column (outer, 2 * inner + re/im).  The contraction index is (outer, run of `run`
+// floats): a "contiguous" operand holds the run of a row as consecutive floats (16-byte loads), a
+// "strided" one holds it as complex pairs `stride` floats apart (two 8-byte loads per chunk).
+enum TcOp : int { kTcFwd = 0, kTcGradX = 1, kTcGradY = 2 };
+
 struct MmTcParams {
-  const float* x;   // [nspec, nb, fi, 2]
-  const float* y;   // [nspec, fi, fo, 2]
-  float* z;         // [nspec, nb, fo, 2]
+  const float* a;   // operand read along the output rows
+  const float* b;   // operand read along the output columns
+  float* c;         // output
   int nl, nb, fi, fo;
+  int run;          // floats per outer contraction index: 2 fi (fwd), 2 fo (grad x), 2 nb (grad y)
   int kblk;         // floats per K block (multiple of 8, <= kTcKMax)
-  int nblk;         // K blocks per p
+  int nblk;         // K blocks per run
   int* err;         // device flag, set to 1 on a wait time-out
 };
+
+// row / column geometry of one degree
+struct TcGeom {
+  int RI;           // inner extent of a row index
+  int CW;           // floats per outer column index (2 * inner extent)
+};
+__host__ __device__ __forceinline__ TcGeom tc_geom(int op, int nb, int fi, int fo) {
+  TcGeom g;
+  g.RI = op == kTcGradY ? fi : nb;
+  g.CW = op == kTcGradX ? 2 * fi : 2 * fo;
+  return g;
+}
 
 constexpr int kTcBM = 128, kTcBN = 128;
 constexpr int kTcKMax = 48;                       // floats per K block
@@ -50,6 +81,9 @@ constexpr int kTcBufBytes = (kTcKMax / 4) * kTcLBO;   // one operand buffer (hi 
 constexpr int kTcStageBytes = 4 * kTcBufBytes;        // A hi, A lo, B hi, B lo
 constexpr int kTcSmemBytes = 2 * kTcStageBytes + 64;
 constexpr int kTcThreads = 512;
+// K blocks accumulated in tensor memory before the partial sum moves to FP32 registers (bounds the
+// length of the tensor core's own accumulation chain, whose additions truncate)
+constexpr int kTcFlushBlocks = 16;
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -128,45 +162,90 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ long tc_tiles_for(const MmTcParams& p, int l) {
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const float (&v)[16]) {
+  uint32_t r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(v[i]);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__host__ __device__ __forceinline__ long tc_tiles_for(int op, int nb, int fi, int fo, int l) {
+  const TcGeom g = tc_geom(op, nb, fi, fo);
   const long L = 2 * l + 1;
-  const long M = L * p.nb, N = L * p.fo * 2;
+  const long M = L * g.RI, N = L * g.CW;
   return ((M + kTcBM - 1) / kTcBM) * ((N + kTcBN - 1) / kTcBN);
 }
 
+// FLUSH = false drops the partial-sum code (fewer registers); valid while no degree needs more than
+// kTcFlushBlocks K blocks.
+template <int OP, bool FLUSH>
 __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(s2c_dyn_smem);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + 2 * kTcStageBytes);      // [2]
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + 2 * kTcStageBytes);      // [2] stages
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 2 * kTcStageBytes + 16);
+  uint64_t* flushbar = reinterpret_cast<uint64_t*>(smem + 2 * kTcStageBytes + 32);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---- which tile ---------------------------------------------------------------------------
   int l = p.nl - 1;
   long t = blockIdx.x;
   for (;; --l) {
-    const long c = tc_tiles_for(p, l);
+    const long c = tc_tiles_for(OP, p.nb, p.fi, p.fo, l);
     if (t < c) break;
     t -= c;
   }
   const int L = 2 * l + 1;
-  const int M = L * p.nb, Np = L * p.fo * 2;
+  const TcGeom geo = tc_geom(OP, p.nb, p.fi, p.fo);
+  const int RI = geo.RI, CW = geo.CW;
+  const int M = L * RI, Np = L * CW;
   const int tiles_n = (Np + kTcBN - 1) / kTcBN;
   const int row0 = (int)(t / tiles_n) * kTcBM, col0 = (int)(t % tiles_n) * kTcBN;
   const long spec0 = (long)l * (4L * l * l - 1) / 3;
   const int fi2 = 2 * p.fi, fo2 = 2 * p.fo;
+  // operand addressing (floats): offset of outer contraction index `o`, element `kf` of its run =
+  //   contiguous:  o * ko + kf          strided:  o * ko + (kf / 2) * st + (kf % 2)
+  constexpr bool a_str = OP == kTcGradY, b_str = OP != kTcGradX;
+  long a_ko, b_ko, a_st = 0, b_st = 0;
+  if (OP == kTcFwd)        { a_ko = (long)p.nb * fi2;      b_ko = (long)p.fi * fo2;      b_st = fo2; }
+  else if (OP == kTcGradX) { a_ko = (long)p.nb * fo2;      b_ko = (long)L * p.fi * fo2; }
+  else                       { a_ko = (long)L * p.nb * fi2;  b_ko = (long)L * p.nb * fo2;  a_st = fi2; b_st = fo2; }
 
   // ---- set-up: barriers, tensor memory ------------------------------------------------------
   if (tid == 0) {
     tc_mbar_init(&mbar[0], 1);
     tc_mbar_init(&mbar[1], 1);
+    tc_mbar_init(flushbar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
     __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      tc_smem_u32(tmem_slot)),
-                 "r"(kTcBN)
+                 "r"(2 * kTcBN)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -184,59 +263,73 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
 
   // Per-thread staging slots.  The (row, 16-byte chunk) handled by a slot and the part of its
   // global offset that does not change along K are computed once; the K loop only adds the offset
-  // of block (p, slice).  Slots are laid out for the full block width kblk; chunks past the end of
-  // a shorter last slice are staged as zeros.
+  // of block (outer index, slice of the run).  Slots are laid out for the full block width kblk;
+  // chunks past the end of a shorter last slice are staged as zeros.  A contiguous operand maps
+  // consecutive threads to consecutive chunks of one row (coalesced 16-byte loads), a strided one
+  // to consecutive rows (neighbouring 8-byte loads).
   constexpr int kSlots = kTcBM * (kTcKMax / 4) / kTcThreads;  // 6 for A and 6 for B
   const int nchf = p.kblk / 4;                                 // chunks per full block
   long offA[kSlots], offB[kSlots];
-  int soA[kSlots], soB[kSlots], chA[kSlots], kqB[kSlots];
-  float4 ra[kSlots];
-  float2 rb0[kSlots], rb1[kSlots];
+  int soA[kSlots], soB[kSlots], chA[kSlots], chB[kSlots];
+  unsigned oddB = 0;                                           // bit q: slot q stages an "imaginary" column
+  float4 ra[kSlots], rb[kSlots];
 #pragma unroll
   for (int q = 0; q < kSlots; ++q) {
     const int e = tid + kTcThreads * q;
-    {  // A: consecutive threads -> consecutive chunks of one row (coalesced 16-byte loads)
-      const int r = e / nchf, ch = e - r * nchf;
+    {
+      int r, ch;
+      if (a_str) { r = e % kTcBM; ch = e / kTcBM; } else { r = e / nchf; ch = e - r * nchf; }
       const int gr = row0 + r;
-      chA[q] = (r < kTcBM && gr < M) ? ch : -1;
-      const int m = gr / p.nb, i = gr - m * p.nb;
-      offA[q] = (((spec0 + (long)m * L) * p.nb + i) * fi2) + 4 * ch;
+      chA[q] = (r < kTcBM && ch < nchf && gr < M) ? ch : -1;
+      const int ro = gr / RI, ri = gr - ro * RI;
+      long base;
+      if (OP == kTcFwd)        base = ((spec0 + (long)ro * L) * p.nb + ri) * fi2;
+      else if (OP == kTcGradX) base = ((spec0 + (long)ro * L) * p.nb + ri) * fo2;
+      else                       base = (spec0 + ro) * p.nb * fi2 + 2 * ri;
+      offA[q] = base + (a_str ? (long)(2 * ch) * a_st : 4 * ch);
       soA[q] = ch * kTcLBO + r * 16;
     }
-    {  // B': consecutive threads -> consecutive rows (n, j, c); each stages one 16-byte chunk
-      const int rr = e % kTcBN, kq = e / kTcBN;
+    {
+      int rr, ch;
+      if (b_str) { rr = e % kTcBN; ch = e / kTcBN; } else { rr = e / nchf; ch = e - rr * nchf; }
       const int gcol = col0 + rr;
-      kqB[q] = (kq < nchf && gcol < Np) ? kq : -1;
-      const int n = gcol / fo2, j = (gcol - n * fo2) >> 1;
-      offB[q] = ((spec0 + (long)n * L) * p.fi * p.fo + j) * 2;
-      soB[q] = kq * kTcLBO + rr * 16;
+      chB[q] = (rr < kTcBN && ch < nchf && gcol < Np) ? ch : -1;
+      const int co = gcol / CW, rem = gcol - co * CW;
+      const int in = rem >> 1;
+      if (rem & 1) oddB |= 1u << q;
+      long base;
+      if (OP == kTcFwd)        base = ((spec0 + (long)co * L) * p.fi * p.fo + in) * 2;
+      else if (OP == kTcGradX) base = ((spec0 + co) * p.fi + in) * fo2;
+      else                       base = (spec0 + co) * p.nb * fo2 + 2 * in;
+      offB[q] = base + (b_str ? (long)(2 * ch) * b_st : 4 * ch);
+      soB[q] = ch * kTcLBO + rr * 16;
     }
   }
-  const bool imag_row = (tid & 1) != 0;  // rr and tid have the same parity (kTcThreads, kTcBN even)
 
-  auto block_geom = [&](int it, int& pidx, int& k0, int& kvalid) {
-    pidx = it / p.nblk;
-    const int kb = it - pidx * p.nblk;
+  auto block_geom = [&](int it, int& oidx, int& k0, int& kvalid) {
+    oidx = it / p.nblk;
+    const int kb = it - oidx * p.nblk;
     k0 = kb * p.kblk;
-    kvalid = (fi2 - k0) < p.kblk ? (fi2 - k0) : p.kblk;   // floats with data (multiple of 4)
+    kvalid = (p.run - k0) < p.kblk ? (p.run - k0) : p.kblk;   // floats with data (multiple of 4)
+  };
+  // four consecutive K floats of one row: (re, im) of two complex numbers
+  auto load4 = [&](const float* src, bool strided, long st) {
+    if (!strided) return __ldg(reinterpret_cast<const float4*>(src));
+    const float2 u = __ldg(reinterpret_cast<const float2*>(src));
+    const float2 w = __ldg(reinterpret_cast<const float2*>(src + st));
+    return make_float4(u.x, u.y, w.x, w.y);
   };
   auto prefetch = [&](int it) {
-    int pidx, k0, kvalid;
-    block_geom(it, pidx, k0, kvalid);
-    const long pa = (long)pidx * p.nb * fi2 + k0;
-    const long pb = ((long)pidx * p.fi + (k0 >> 1)) * p.fo * 2;
+    int oidx, k0, kvalid;
+    block_geom(it, oidx, k0, kvalid);
+    const long pa = (long)oidx * a_ko + (a_str ? (long)(k0 >> 1) * a_st : k0);
+    const long pb = (long)oidx * b_ko + (b_str ? (long)(k0 >> 1) * b_st : k0);
 #pragma unroll
     for (int q = 0; q < kSlots; ++q) {
       ra[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (chA[q] >= 0 && 4 * chA[q] < kvalid)
-        ra[q] = __ldg(reinterpret_cast<const float4*>(p.x + offA[q] + pa));
-      rb0[q] = make_float2(0.f, 0.f);
-      rb1[q] = make_float2(0.f, 0.f);
-      if (kqB[q] >= 0 && 4 * kqB[q] < kvalid) {  // complex k = 2 kq and 2 kq + 1 of this block
-        const float* src = p.y + offB[q] + pb + (long)(2 * kqB[q]) * p.fo * 2;
-        rb0[q] = __ldg(reinterpret_cast<const float2*>(src));
-        rb1[q] = __ldg(reinterpret_cast<const float2*>(src + p.fo * 2));
-      }
+      if (chA[q] >= 0 && 4 * chA[q] < kvalid) ra[q] = load4(p.a + offA[q] + pa, a_str, a_st);
+      rb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (chB[q] >= 0 && 4 * chB[q] < kvalid) rb[q] = load4(p.b + offB[q] + pb, b_str, b_st);
     }
   };
   // v = hi + lo with hi carrying the 10 explicit TF32 mantissa bits (the tensor core ignores the
@@ -254,12 +347,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     *reinterpret_cast<float4*>(hi_buf + so) = hi;
     *reinterpret_cast<float4*>(lo_buf + so) = lo;
   };
+  // Real rows of the column operand, per complex number (a, b) of the run:
+  //   fwd, grad y (conjugated operand):  even column (a, b)    odd column (-b, a)
+  //   grad x (plain product):            even column (a, -b)   odd column ( b, a)
+  constexpr bool conj_b = OP != kTcGradX;
+  auto column_rows = [&](float4 v, bool odd) {
+    if (conj_b) return odd ? make_float4(-v.y, v.x, -v.w, v.z) : v;
+    return odd ? make_float4(v.y, v.x, v.w, v.z) : make_float4(v.x, -v.y, v.z, -v.w);
+  };
+
+  // This thread's share of the accumulator (TMEM lanes 32 (warp % 4) + lane, 32 columns).  Partial
+  // sums leave the MMA accumulator every kTcFlushBlocks K blocks and are added up in FP32 by the
+  // threads in a second tensor-memory region (columns kTcBN .. 2 kTcBN - 1).
+  constexpr int kColGroups = kTcThreads / 128;
+  constexpr int kColsPerWarp = kTcBN / kColGroups;
+  static_assert(kColsPerWarp == 32, "one tcgen05.ld of 32 columns per warp");
+  const uint32_t tmem_mine = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) +
+                             (uint32_t)(kColsPerWarp * (warp >> 2));
+  bool have_sum = false, pending_flush = false;
+  uint32_t flush_parity = 0;
+  bool fresh = true;   // the next MMA starts a new accumulation in tensor memory
 
   prefetch(0);
   for (int it = 0; it < nit; ++it) {
     const int s = it & 1;
-    int pidx, k0, kvalid;
-    block_geom(it, pidx, k0, kvalid);
+    int oidx, k0, kvalid;
+    block_geom(it, oidx, k0, kvalid);
     const int ksteps = (kvalid + 7) / 8;
     unsigned char* stage = smem + (size_t)s * kTcStageBytes;
     unsigned char* Ahi = stage;
@@ -274,14 +387,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
 #pragma unroll
     for (int q = 0; q < kSlots; ++q) {
       const int e = tid + kTcThreads * q;
-      if (e < kTcBM * nchf) split_store(Ahi, Alo, soA[q], ra[q]);
-      if (e < kTcBN * nchf) {
-        // row (j,0) = (yr, yi) per complex k;  row (j,1) = (-yi, yr)   [x * conj(y)]
-        const float2 a = rb0[q], b = rb1[q];
-        const float4 v = imag_row ? make_float4(-a.y, a.x, -b.y, b.x)
-                                  : make_float4(a.x, a.y, b.x, b.y);
-        split_store(Bhi, Blo, soB[q], v);
+      if (e < kTcBM * nchf) {
+        split_store(Ahi, Alo, soA[q], ra[q]);
+        split_store(Bhi, Blo, soB[q], column_rows(rb[q], (oddB >> q) & 1u));
       }
+    }
+    if (FLUSH && pending_flush) {
+      if (!tc_mbar_wait(flushbar, flush_parity)) ok = false;
+      flush_parity ^= 1u;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {       // 16 columns at a time keeps the transient registers low
+        float v[16];
+        tc_ld16(tmem_mine + 16 * h, v);
+        if (have_sum) {
+          float w[16];
+          tc_ld16(tmem_mine + kTcBN + 16 * h, w);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += w[i];
+        }
+        tc_st16(tmem_mine + kTcBN + 16 * h, v);
+      }
+      have_sum = true;
+      // the block barrier below orders these reads before the MMA that restarts the accumulator
     }
     if (it + 1 < nit) prefetch(it + 1);
     // make the generic-proxy writes visible to the tensor core (async proxy), then hand over
@@ -296,12 +424,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
         const uint32_t koff = (uint32_t)ks * 2u * kTcLBO;
         const uint64_t dah = tc_smem_desc(a_hi + koff), dal = tc_smem_desc(a_lo + koff);
         const uint64_t dbh = tc_smem_desc(b_hi + koff), dbl = tc_smem_desc(b_lo + koff);
-        tc_mma_tf32(tmem_base, dah, dbh, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+        tc_mma_tf32(tmem_base, dah, dbh, idesc, (fresh && ks == 0) ? 0u : 1u);
         tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
         tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
       }
       tc_commit(&mbar[s]);
     }
+    // every kTcFlushBlocks blocks the partial sum leaves the MMA accumulator (handled at the top
+    // of the next iteration, where the staging registers are free)
+    pending_flush = FLUSH && ((it + 1) % kTcFlushBlocks == 0) && (it + 1 < nit);
+    fresh = pending_flush;
+    if (pending_flush && tid == 0) tc_commit(flushbar);   // arrives when every MMA so far has finished
   }
 
   // ---- wait for the last commit (it covers every earlier MMA of the issuing thread) ----------
@@ -321,23 +454,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   if (ok) {
     // warp w may only touch TMEM lanes 32 (w % 4) .. +31; the warps sharing a lane quarter split
     // the 128 accumulator columns between them
-    constexpr int kColGroups = kTcThreads / 128;
-    constexpr int kColsPerWarp = kTcBN / kColGroups;
     const int q = warp & 3, cg = warp >> 2;
     const int r = row0 + 32 * q + lane;
-    const int m = r / p.nb, i = r - m * p.nb;
+    const int ro = r / RI, ri = r - ro * RI;
+    // c[((spec0 + ro * sro + co * sco) * RI + ri) * CW + rem]
+    const int sro = OP == kTcGradY ? 1 : L, sco = OP == kTcGradY ? L : 1;
 #pragma unroll 1
     for (int g = 0; g < kColsPerWarp / 32; ++g) {
       const int cbase = kColsPerWarp * cg + 32 * g;
       float v[32];
       tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)cbase, v);
+      if (FLUSH && have_sum) {
+        float w[32];
+        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTcBN + cbase), w);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] += w[i];
+      }
       if (r < M) {
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const int gcol = col0 + cbase + 4 * c4;
           if (gcol < Np) {  // Np is a multiple of 4, so a group of 4 is all in or all out
-            const int n = gcol / fo2, rem = gcol - n * fo2;
-            float* dst = p.z + ((spec0 + (long)m * L + n) * p.nb + i) * fo2 + rem;
+            const int co = gcol / CW, rem = gcol - co * CW;
+            float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
             *reinterpret_cast<float4*>(dst) =
                 make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
           }
@@ -353,23 +492,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   __syncthreads();
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(kTcBN)
+                 "r"(2 * kTcBN)
                  : "memory");
   }
 }
 
-inline bool so3_mm_tc_supported(int nl, int nb, int fi, int fo) {
-  (void)nl;
-  (void)nb;
+// 16-byte accesses need: the run of the contraction index and the column width multiples of 4
+// floats.  fwd and grad x: f_in and f_out even; grad y: batch and f_out even.
+inline bool so3_mm_tc_supported(int op, int nb, int fi, int fo) {
+  if (op == kTcGradY) return (nb % 2 == 0) && (fo % 2 == 0);
   return (fi % 2 == 0) && (fo % 2 == 0);
 }
 
-inline long so3_mm_tc_tiles(int nl, int nb, int fo) {
+inline long so3_mm_tc_tiles(int op, int nl, int nb, int fi, int fo) {
   long t = 0;
-  for (int l = 0; l < nl; ++l) {
-    const long L = 2 * l + 1;
-    t += ((L * nb + kTcBM - 1) / kTcBM) * ((L * fo * 2 + kTcBN - 1) / kTcBN);
-  }
+  for (int l = 0; l < nl; ++l) t += tc_tiles_for(op, nb, fi, fo, l);
   return t;
 }
 

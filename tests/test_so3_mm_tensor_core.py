@@ -32,3 +32,55 @@ def test_so3_mm_tensor_core_matches_oracle(nl, nb, fi, fo):
     finally:
         _lib.cuda_lib().s2c_debug_force_general_path(0)
     assert_close(z, z_simt, "tcgen05 vs FP32 kernel")
+
+
+def _grad_reference(x, y, gz, nl):
+    """Gradients of z = so3_mm(x, y) by complex arithmetic in float64 (s2cnn/so3_mm.py:40-61):
+    gx[l,m,p,i,k] = sum_{n,j} gz[l,m,n,i,j] y[l,n,p,k,j],  gy[l,n,p,k,j] = sum_{m,i} conj(gz) x."""
+    xc = torch.view_as_complex(x.double().contiguous())
+    yc = torch.view_as_complex(y.double().contiguous())
+    gc = torch.view_as_complex(gz.double().contiguous())
+    gx, gy = torch.zeros_like(xc), torch.zeros_like(yc)
+    for l in range(nl):
+        L, o = 2 * l + 1, O.so3_offset(l)
+        xl = xc[o:o + L * L].reshape(L, L, *xc.shape[1:])      # [m, p, i, k]
+        yl = yc[o:o + L * L].reshape(L, L, *yc.shape[1:])      # [n, p, k, j]
+        gl = gc[o:o + L * L].reshape(L, L, *gc.shape[1:])      # [m, n, i, j]
+        gx[o:o + L * L] = torch.einsum("mnij,npkj->mpik", gl, yl).reshape(L * L, *xc.shape[1:])
+        gy[o:o + L * L] = torch.einsum("mnij,mpik->npkj", gl.conj(), xl).reshape(L * L, *yc.shape[1:])
+    return torch.view_as_real(gx).float(), torch.view_as_real(gy).float()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nl,nb,fi,fo", [(6, 256, 20, 40), (3, 130, 26, 6), (4, 100, 4, 64),
+                                         (1, 2, 2, 2), (5, 4, 18, 2), (2, 300, 50, 10),
+                                         (3, 64, 7, 10)])
+def test_so3_mm_gradients_on_tensor_cores(nl, nb, fi, fo):
+    """Both gradient products through the same tcgen05 kernel (row / column addressing and sign
+    pattern per product) against float64 complex arithmetic and against the FP32 kernel; the last
+    shape has an odd f_in, which only the grad-y product accepts."""
+    from s2cnn_b200 import _lib
+    from s2cnn_b200.ops import cuda_ops
+    ops = cuda_ops()
+    lib = _lib.cuda_lib()
+    gen = torch.Generator().manual_seed(nl * 11 + fo)
+    x = torch.randn(n3(nl), nb, fi, 2, generator=gen)
+    y = torch.randn(n3(nl), fi, fo, 2, generator=gen)
+    gz = torch.randn(n3(nl), nb, fo, 2, generator=gen)
+    ref_gx, ref_gy = _grad_reference(x, y, gz, nl)
+    n0 = lib.s2c_launch_count()
+    gx = ops.so3_mm_gradx(gz.cuda(), y.cuda(), nb, fi)
+    gy = ops.so3_mm_grady(gz.cuda(), x.cuda(), fo)
+    torch.cuda.synchronize()
+    assert lib.s2c_launch_count() - n0 == 2
+    assert lib.s2c_so3_mm_tc_status() == 0
+    assert_close(gx, ref_gx, "grad x")
+    assert_close(gy, ref_gy, "grad y")
+    lib.s2c_debug_force_general_path(1)
+    try:
+        gx_simt = ops.so3_mm_gradx(gz.cuda(), y.cuda(), nb, fi)
+        gy_simt = ops.so3_mm_grady(gz.cuda(), x.cuda(), fo)
+    finally:
+        lib.s2c_debug_force_general_path(0)
+    assert_close(gx, gx_simt, "grad x: tcgen05 vs FP32 kernel")
+    assert_close(gy, gy_simt, "grad y: tcgen05 vs FP32 kernel")
