@@ -15,6 +15,7 @@
 #include "so3_fused_kernels.h"
 #include "wigner_tiled.h"
 #include "cgemm_kernels.h"
+#include "s2_mm_thin.h"
 #include "so3_mm_tc.h"
 #include "misc_kernels.h"
 
@@ -701,11 +702,28 @@ int s2c_s2_mm(const float* x, const float* y, float* z, int nl, int nb, int fi, 
 int s2c_s2_mm_gradx(const float* gz, const float* y, float* gx, int nl, int nb, int fi, int fo,
                     void* st) {
   if (!gz || !y || !gx) return fail(S2C_ERR_BAD_ARG, "s2c_s2_mm_gradx: null pointer");
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+  if (!g_force_general && s2_mm_thin_supported(nl, fi, fo)) {
+    S2ThinParams p;
+    p.gz = (const float2*)gz; p.other = (const float2*)y; p.out = (float2*)gx;
+    p.nl = nl; p.nb = nb; p.fi = fi; p.fo = fo;
+    const long blocks = (long)nl * nl * ((nb + kThinRows - 1) / kThinRows);
+    return S2C_LAUNCH(s2_mm_gradx_thin, blocks, kThinRows * kThinSlices,
+                      s2_gradx_thin_smem(nl, fi, fo), as_stream(st), p);
+  }
   return mm_dispatch(false, kMmGradX, gz, y, gx, nl, nb, fi, fo, as_stream(st));
 }
 int s2c_s2_mm_grady(const float* gz, const float* x, float* gy, int nl, int nb, int fi, int fo,
                     void* st) {
   if (!gz || !x || !gy) return fail(S2C_ERR_BAD_ARG, "s2c_s2_mm_grady: null pointer");
+  if (nl < 1 || nb < 1 || fi < 1 || fo < 1) return fail(S2C_ERR_BAD_ARG, "sizes must be >= 1");
+  if (!g_force_general && s2_mm_thin_supported(nl, fi, fo)) {
+    S2ThinParams p;
+    p.gz = (const float2*)gz; p.other = (const float2*)x; p.out = (float2*)gy;
+    p.nl = nl; p.nb = nb; p.fi = fi; p.fo = fo;
+    return S2C_LAUNCH(s2_mm_grady_thin, (long)nl * nl, s2_grady_thin_threads(fo),
+                      s2_grady_thin_smem(fo), as_stream(st), p);
+  }
   return mm_dispatch(false, kMmGradY, x, gz, gy, nl, nb, fi, fo, as_stream(st));
 }
 
