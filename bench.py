@@ -105,10 +105,9 @@ def kernel_bytes(B):
     sig1 = B * f1 * (2 * b1) ** 3 * 4   # conv1 output / conv2 input signal
     sig2 = B * f2 * (2 * b2) ** 3 * 4   # conv2 output signal
     out = {}
-    # S2 analysis of the input (two small passes of the general kernels, n = 0 only)
-    N0, K0 = 2 * b0, b1
-    out["so3_fwd_alpha"] = B * f0 * N0 * N0 * 4 + (2 * K0 - 1) * B * f0 * N0 * c
-    out["so3_fwd_wigner"] = (2 * K0 - 1) * B * f0 * N0 * c + b1 * b1 * B * f0 * c
+    # S2 analysis of the real input in one kernel: reads the signal, writes the S2 spectrum
+    N0 = 2 * b0
+    out["s2_fwd_fused"] = B * f0 * N0 * N0 * 4 + b1 * b1 * B * f0 * c
     # kernel-grid -> spectrum transforms of both layers
     out["rft_forward"] = (f0 * f1 * 24 * 4 + b1 * b1 * f0 * f1 * c) + (f1 * f2 * 192 * 4 + n3(b2) * f1 * f2 * c)
     # conv1: s2_mm fused into the synthesis (reads the two S2 spectra, writes the signal)

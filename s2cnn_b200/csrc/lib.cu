@@ -12,6 +12,7 @@
 #include "fft_device.h"
 #include "so3_kernels.h"
 #include "so3_plane_kernels.h"
+#include "s2_fused_kernels.h"
 #include "so3_fused_kernels.h"
 #include "wigner_tiled.h"
 #include "cgemm_kernels.h"
@@ -550,6 +551,13 @@ int s2c_s2_fft(const float* x, int x_is_real, float* out, long nbatch, int b_in,
   PanelsDev pan;
   S2C_TRY(TableCache::get().fft(N, fft));
   S2C_TRY(TableCache::get().panels(b_in, b_out, K, !for_grad, true, pan));
+  if (!g_force_general && x_is_real && N % 2 == 0 && s2_fwd_fused_smem(N) <= 96 * 1024) {
+    // real signal whose packed half plane fits in shared memory: one kernel, no scratch
+    S2FwdFusedParams f;
+    f.x = x; f.out = (float2*)out; f.out_zstride = nbatch;
+    f.pan = pan; f.fft = fft; f.N = N; f.K = K;
+    return S2C_LAUNCH(s2_fwd_fused, nbatch, kThreads, s2_fwd_fused_smem(N), st, f);
+  }
   const size_t per_z = s2_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || !ws) return fail(S2C_ERR_WORKSPACE, "s2c_s2_fft: workspace too small");

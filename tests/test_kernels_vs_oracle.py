@@ -100,6 +100,29 @@ def test_s2_fft_golden(backend, name):
     xr = g["x"][..., 0].contiguous()
     ref = O.s2_fft(torch.stack((xr, torch.zeros_like(xr)), -1), b_out=int(g["b_out"]))
     assert_close(ops.s2_fft(xr.to(dev), b_out=int(g["b_out"]), x_is_real=True), ref, name + " real")
+    # real input takes the single-kernel analysis; the two-kernel path must give the same values
+    ops.lib.s2c_debug_force_general_path(1)
+    try:
+        assert_close(ops.s2_fft(xr.to(dev), b_out=int(g["b_out"]), x_is_real=True), ref,
+                     name + " real, two kernels")
+    finally:
+        ops.lib.s2c_debug_force_general_path(0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(30, 10, 3), (32, 32, 2), (7, 3, 5), (1, 1, 2)])
+def test_s2_fft_real_single_kernel(backend, b_in, b_out, nbatch):
+    """The single-kernel S2 analysis of a real signal (packed row pairs, generic and two-step row
+    FFTs), both weightings, at the first-layer size of the benchmark network among others."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in * 3 + b_out)
+    x = torch.randn(nbatch, 2 * b_in, 2 * b_in, generator=gen)
+    for fg in (False, True):
+        ref = O.s2_fft(torch.stack((x, torch.zeros_like(x)), -1), for_grad=fg, b_out=b_out)
+        n0 = ops.lib.s2c_launch_count()
+        got = ops.s2_fft(x.to(dev), fg, b_out, x_is_real=True)
+        assert ops.lib.s2c_launch_count() - n0 == 1
+        assert_close(got, ref, "s2_fft real for_grad=%s" % fg)
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
