@@ -34,3 +34,78 @@ class GraphedForward:
         self.static_in.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.static_out
+
+
+class PipelinedForward:
+    """Inference on batches that arrive in pinned host memory, with the host-to-device copy of the
+    next batch overlapped with the forward pass of the current one.
+
+    Two captured copies of the forward pass (``GraphedForward``) alternate; a copy stream uploads
+    batch i + 1 into the idle copy's input buffer while the compute stream replays the graph on
+    batch i and returns its result to pinned host memory.  ``submit`` never blocks the host;
+    ``wait`` blocks until everything submitted so far has reached the host.
+
+        pipe = PipelinedForward(net, example_device_batch)
+        for x_host, y_host in zip(batches, results):      # pinned tensors
+            pipe.submit(x_host, y_host)
+        pipe.wait()
+    """
+
+    def __init__(self, module, example_input, depth=2):
+        assert depth >= 2
+        dev = example_input.device
+        self.device = dev
+        self.slots = [GraphedForward(module, example_input) for _ in range(depth)]
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.uploaded = [torch.cuda.Event() for _ in range(depth)]
+        self.consumed = [torch.cuda.Event() for _ in range(depth)]   # slot's input buffer is free again
+        self.n_uploaded = 0
+        self.n_run = 0
+
+    def prefetch(self, x_host):
+        """Start the upload of the next batch (pinned host tensor) on the copy stream."""
+        slot = self.n_uploaded % len(self.slots)
+        if self.n_uploaded >= len(self.slots):
+            self.copy_stream.wait_event(self.consumed[slot])
+        with torch.cuda.stream(self.copy_stream):
+            self.slots[slot].static_in.copy_(x_host, non_blocking=True)
+            self.uploaded[slot].record(self.copy_stream)
+        self.n_uploaded += 1
+
+    def join_uploads(self):
+        """Make the current stream wait for the most recent upload (so that an event recorded next
+        on the current stream also covers that upload)."""
+        if self.n_uploaded:
+            slot = (self.n_uploaded - 1) % len(self.slots)
+            torch.cuda.current_stream(self.device).wait_event(self.uploaded[slot])
+
+    def run(self, y_host):
+        """Forward pass on the oldest uploaded batch; the result is copied into ``y_host`` (pinned)
+        asynchronously on the current stream."""
+        assert self.n_run < self.n_uploaded, "run() without a prefetched batch"
+        slot = self.n_run % len(self.slots)
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_event(self.uploaded[slot])
+        g = self.slots[slot]
+        g.graph.replay()
+        self.consumed[slot].record(cur)
+        y_host.copy_(g.static_out, non_blocking=True)
+        self.n_run += 1
+
+    def submit(self, x_host, y_host):
+        """Upload ``x_host`` and run every batch that is ready but one, so that one upload is always
+        in flight behind the forward pass; call ``flush`` for the results of the last batch."""
+        self.prefetch(x_host)
+        self._pending = getattr(self, "_pending", [])
+        self._pending.append(y_host)
+        while len(self._pending) > 1:
+            self.run(self._pending.pop(0))
+
+    def flush(self):
+        for y in getattr(self, "_pending", []):
+            self.run(y)
+        self._pending = []
+
+    def wait(self):
+        self.flush()
+        torch.cuda.synchronize(self.device)
