@@ -638,7 +638,7 @@ static __device__ int g_tc_err_flag;
 // so3_mm or one of its gradients on the tensor cores; `handled` tells whether the shape qualified.
 static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, int nl, int nb, int fi,
                             int fo, stream_t st, bool* handled) {
-  *handled = !g_force_general && so3_mm_tc_supported(op, nb, fi, fo);
+  *handled = !g_force_general;
   if (!*handled) return S2C_OK;
   MmTcParams p;
   p.a = a; p.b = b; p.c = c;
@@ -651,12 +651,15 @@ static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, in
   p.err = (int*)flag;
   const long tiles = so3_mm_tc_tiles(op, nl, nb, fi, fo);
   const bool flush = (long)(2 * nl - 1) * p.nblk > kTcFlushBlocks;   // longest K loop of any degree
-#define S2C_TC_LAUNCH(OP, NAME)                                                                   \
-  (flush ? launch_impl(so3_mm_tc_kernel<OP, true>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p)   \
-         : launch_impl(so3_mm_tc_kernel<OP, false>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p))
+  const bool vec = so3_mm_tc_vec16(op, nb, fi, fo);
+#define S2C_TC_LAUNCH2(OP, FL, NAME)                                                               \
+  (vec ? launch_impl(so3_mm_tc_kernel<OP, FL, true>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p)  \
+       : launch_impl(so3_mm_tc_kernel<OP, FL, false>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p))
+#define S2C_TC_LAUNCH(OP, NAME) (flush ? S2C_TC_LAUNCH2(OP, true, NAME) : S2C_TC_LAUNCH2(OP, false, NAME))
   if (op == kTcFwd) return S2C_TC_LAUNCH(kTcFwd, "so3_mm_tc_kernel");
   if (op == kTcGradX) return S2C_TC_LAUNCH(kTcGradX, "so3_mm_tc_gradx");
   return S2C_TC_LAUNCH(kTcGradY, "so3_mm_tc_grady");
+#undef S2C_TC_LAUNCH2
 #undef S2C_TC_LAUNCH
 }
 #endif

@@ -1,5 +1,5 @@
-// Gradients of s2_mm for layers with few input features (f_in <= kThinFi; the first layer of the
-// reference's models has 1 to 6):
+// Gradients of s2_mm for layers with few input features (f_in <= kThinFi = 8; the first layer of
+// the reference's models has 1 to 6):
 //   gx[l,m,i,k] = sum_{n,j} gz[l,m,n,i,j] y[l,n,k,j]            (s2cnn/s2_mm.py:38-46, kernel :222-262)
 //   gy[l,n,k,j] = sum_{m,i} conj(gz[l,m,n,i,j]) x[l,m,i,k]      (s2cnn/s2_mm.py:48-58, kernel :265-312)
 // With f_in that small both are reductions over the large tensor gz with a handful of outputs per
@@ -13,7 +13,7 @@
 
 namespace s2c {
 
-constexpr int kThinFi = 4;           // largest f_in these kernels take
+constexpr int kThinFi = 8;           // largest f_in these kernels take
 constexpr int kThinRows = 64;        // batch rows per block of the grad-x kernel
 constexpr int kThinSlices = 4;       // slices of the n range per block of the grad-x kernel
 
@@ -104,7 +104,7 @@ inline size_t s2_grady_thin_smem(int fo) {
 }
 
 // block = (l, n); thread = (slice of the batch rows, j); all of (m, i) is summed inside the block
-S2C_KERNEL(s2_mm_grady_thin, S2ThinParams) {
+S2C_KERNEL_BOUNDS(s2_mm_grady_thin, S2ThinParams, 1024, 1) {
   const int l = thin_isqrt(ctx.bid), n = ctx.bid - l * l;
   const int L = 2 * l + 1;
   const int nsl = ctx.nthr / p.fo;

@@ -201,7 +201,9 @@ __host__ __device__ __forceinline__ long tc_tiles_for(int op, int nb, int fi, in
 
 // FLUSH = false drops the partial-sum code (fewer registers); valid while no degree needs more than
 // kTcFlushBlocks K blocks.
-template <int OP, bool FLUSH>
+// VEC = true: 16-byte loads and stores (feature counts - for grad y the batch - even); VEC = false:
+// 8-byte accesses, any sizes.
+template <int OP, bool FLUSH, bool VEC>
 __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(s2c_dyn_smem);
@@ -310,13 +312,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     oidx = it / p.nblk;
     const int kb = it - oidx * p.nblk;
     k0 = kb * p.kblk;
-    kvalid = (p.run - k0) < p.kblk ? (p.run - k0) : p.kblk;   // floats with data (multiple of 4)
+    kvalid = (p.run - k0) < p.kblk ? (p.run - k0) : p.kblk;   // floats with data (even; VEC: multiple of 4)
   };
-  // four consecutive K floats of one row: (re, im) of two complex numbers
-  auto load4 = [&](const float* src, bool strided, long st) {
-    if (!strided) return __ldg(reinterpret_cast<const float4*>(src));
+  // four consecutive K floats of one row: (re, im) of two complex numbers; `nvalid` (2 or 4) of them
+  // lie inside the run
+  auto load4 = [&](const float* src, bool strided, long st, int nvalid) {
+    if (VEC && !strided) return __ldg(reinterpret_cast<const float4*>(src));
     const float2 u = __ldg(reinterpret_cast<const float2*>(src));
-    const float2 w = __ldg(reinterpret_cast<const float2*>(src + st));
+    float2 w = make_float2(0.f, 0.f);
+    if (VEC || nvalid > 2) w = __ldg(reinterpret_cast<const float2*>(src + (strided ? st : 2)));
     return make_float4(u.x, u.y, w.x, w.y);
   };
   auto prefetch = [&](int it) {
@@ -327,9 +331,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
 #pragma unroll
     for (int q = 0; q < kSlots; ++q) {
       ra[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (chA[q] >= 0 && 4 * chA[q] < kvalid) ra[q] = load4(p.a + offA[q] + pa, a_str, a_st);
+      if (chA[q] >= 0 && 4 * chA[q] < kvalid)
+        ra[q] = load4(p.a + offA[q] + pa, a_str, a_st, kvalid - 4 * chA[q]);
       rb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (chB[q] >= 0 && 4 * chB[q] < kvalid) rb[q] = load4(p.b + offB[q] + pb, b_str, b_st);
+      if (chB[q] >= 0 && 4 * chB[q] < kvalid)
+        rb[q] = load4(p.b + offB[q] + pb, b_str, b_st, kvalid - 4 * chB[q]);
     }
   };
   // v = hi + lo with hi carrying the 10 explicit TF32 mantissa bits (the tensor core ignores the
@@ -471,14 +477,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
         for (int i = 0; i < 32; ++i) v[i] += w[i];
       }
       if (r < M) {
+        if constexpr (VEC) {
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const int gcol = col0 + cbase + 4 * c4;
-          if (gcol < Np) {  // Np is a multiple of 4, so a group of 4 is all in or all out
-            const int co = gcol / CW, rem = gcol - co * CW;
-            float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
-            *reinterpret_cast<float4*>(dst) =
-                make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const int gcol = col0 + cbase + 4 * c4;
+            if (gcol < Np) {  // CW is a multiple of 4, so a group of 4 is all in or all out
+              const int co = gcol / CW, rem = gcol - co * CW;
+              float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
+              *reinterpret_cast<float4*>(dst) =
+                  make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c2 = 0; c2 < 16; ++c2) {
+            const int gcol = col0 + cbase + 2 * c2;
+            if (gcol < Np) {  // one complex number: never straddles an outer column index
+              const int co = gcol / CW, rem = gcol - co * CW;
+              float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
+              *reinterpret_cast<float2*>(dst) = make_float2(v[2 * c2], v[2 * c2 + 1]);
+            }
           }
         }
       }
@@ -497,9 +515,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   }
 }
 
-// 16-byte accesses need: the run of the contraction index and the column width multiples of 4
-// floats.  fwd and grad x: f_in and f_out even; grad y: batch and f_out even.
-inline bool so3_mm_tc_supported(int op, int nb, int fi, int fo) {
+// 16-byte accesses need the run of the contraction index and the column width to be multiples of 4
+// floats: fwd and grad x: f_in and f_out even; grad y: batch and f_out even.  Other sizes take the
+// 8-byte variant.
+inline bool so3_mm_tc_vec16(int op, int nb, int fi, int fo) {
   if (op == kTcGradY) return (nb % 2 == 0) && (fo % 2 == 0);
   return (fi % 2 == 0) && (fo % 2 == 0);
 }

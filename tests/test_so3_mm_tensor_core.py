@@ -1,6 +1,7 @@
 """The tcgen05 / TMEM implementation of so3_mm (3xTF32) against the oracle, on shapes that
 exercise: the benchmark layer (nl 6, batch 256, 20 -> 40), several K blocks per p (2 f_in > 48),
-row tiles that straddle m, partial row and column tiles, and one degree only.  GPU only - the
+row tiles that straddle m, partial row and column tiles, one degree only, odd feature counts
+(8-byte accesses) and the last layer of the reference's deep configuration (100 -> 255).  GPU only - the
 kernel has no host emulation; the FP32 kernel it replaces is checked on both builds elsewhere."""
 import pytest
 import torch
@@ -13,7 +14,8 @@ n3 = O.so3_nspec
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("nl,nb,fi,fo", [(6, 256, 20, 40), (3, 130, 26, 6), (4, 100, 4, 64),
-                                         (1, 1, 2, 2), (5, 3, 18, 2), (2, 300, 50, 10)])
+                                         (1, 1, 2, 2), (5, 3, 18, 2), (2, 300, 50, 10),
+                                         (4, 33, 7, 9), (3, 5, 1, 1), (5, 32, 100, 255)])
 def test_so3_mm_tensor_core_matches_oracle(nl, nb, fi, fo):
     from s2cnn_b200 import _lib
     from s2cnn_b200.ops import cuda_ops
@@ -54,11 +56,12 @@ def _grad_reference(x, y, gz, nl):
 @pytest.mark.gpu
 @pytest.mark.parametrize("nl,nb,fi,fo", [(6, 256, 20, 40), (3, 130, 26, 6), (4, 100, 4, 64),
                                          (1, 2, 2, 2), (5, 4, 18, 2), (2, 300, 50, 10),
-                                         (3, 64, 7, 10)])
+                                         (3, 64, 7, 10), (4, 33, 7, 9), (3, 5, 1, 1),
+                                         (5, 32, 100, 255)])
 def test_so3_mm_gradients_on_tensor_cores(nl, nb, fi, fo):
     """Both gradient products through the same tcgen05 kernel (row / column addressing and sign
-    pattern per product) against float64 complex arithmetic and against the FP32 kernel; the last
-    shape has an odd f_in, which only the grad-y product accepts."""
+    pattern per product) against float64 complex arithmetic and against the FP32 kernel; odd feature
+    counts or batches take the variant with 8-byte accesses."""
     from s2cnn_b200 import _lib
     from s2cnn_b200.ops import cuda_ops
     ops = cuda_ops()
