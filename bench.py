@@ -8,9 +8,13 @@ classifier  S2Conv(1->20, b 30->10) -> ReLU -> SO3Conv(20->40, b 10->6) -> ReLU 
 Linear(40->10)  on a synthetic batch of 256 N(0,1) signals on the 60x60 sphere grid per GPU,
 random-init weights, float32.  One step = one forward pass over one batch.  The headline metric is
 samples/s; ``value`` is measured with the batch resident in HBM, ``e2e`` through the public module
-API from pinned host memory (host->device copy of the batch and device->host read of the logits
-inside the timed region).  A second object reports the standalone SO(3) FFT round trip at b = 64
-(real [64,128,128,128] -> spectrum -> signal) in GB/s of algorithmic bytes.
+API from pinned host memory (host->device copy of a batch and device->host read of the logits
+inside every timed interval; the copy is that of the NEXT batch, overlapped with the forward pass
+on a copy stream - ``serial_ms_per_step`` gives the same without the overlap).  Further objects on
+the same line (rank 0, one GPU): ``so3_fft_b64`` - the standalone SO(3) FFT round trip at b = 64
+(real [64,128,128,128] -> spectrum -> signal) in GB/s of algorithmic bytes; ``so3_mm_tensor`` - the
+tensor-core spectral product at a GEMM-sized case; ``train_step_c4`` - the training step of the deep
+model among the reference's configurations.
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N``;
 every rank runs the same per-GPU batch (weak scaling, no data-path collective), the time is the max
@@ -382,6 +386,57 @@ def so3_mm_tensor(device, bf16_tf):
             "peak_source": "half of the measured bf16 GEMM peak", "frac": issued / peak}
 
 
+def train_step_c4(device, batch=32, steps=5):
+    """Training step (forward, cross-entropy on uniform random labels, backward) of the deep model
+    among the reference's configurations, batch 32 on one GPU, synthetic input: S2Conv(6->100,
+    b 64->16, max_beta pi/32) -> ReLU -> SO3Conv(100->100, b 16->10) -> ReLU -> SO3Conv(100->255,
+    b 10->5) -> ReLU -> so3_integrate -> Linear(255->55).  (With several ranks the gradients would
+    additionally be summed by s2cnn_b200.parallel.allreduce_gradients; not timed here.)"""
+    import s2cnn_b200 as S
+    g2 = S.s2_near_identity_grid(max_beta=np.pi / 32, n_alpha=8, n_beta=3)
+    g3 = S.so3_near_identity_grid(max_beta=np.pi / 8, max_gamma=2 * np.pi, n_alpha=8, n_beta=3,
+                                  n_gamma=8)
+    torch.manual_seed(4)
+
+    class Deep(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1 = S.S2Convolution(6, 100, 64, 16, g2)
+            self.c2 = S.SO3Convolution(100, 100, 16, 10, g3)
+            self.c3 = S.SO3Convolution(100, 255, 10, 5, g3)
+            self.lin = torch.nn.Linear(255, 55)
+
+        def forward(self, x):
+            x = torch.relu(self.c1(x))
+            x = torch.relu(self.c2(x))
+            x = torch.relu(self.c3(x))
+            return self.lin(S.so3_integrate(x))
+
+    net = Deep().to(device)
+    x = torch.randn(batch, 6, 128, 128, device=device)
+    labels = torch.randint(0, 55, (batch,), device=device)
+
+    def step():
+        net.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.cross_entropy(net(x), labels)
+        loss.backward()
+        return loss
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True)
+    e = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        loss = step()
+    e.record()
+    e.synchronize()
+    ms = a.elapsed_time(e) / steps
+    return {"workload": "deep model 6->100->100->255->55, b 64->16->10->5, batch %d, fwd+bwd" % batch,
+            "ms_per_step": ms, "samples_per_s": batch / (ms * 1e-3), "loss_finite": bool(torch.isfinite(loss))}
+
+
 def run_ours(args):
     world, rank, local = dist_setup(args.gpus)
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback exists)"
@@ -566,6 +621,7 @@ def run_ours(args):
         if world == 1 and not args.skip_fft64:
             line["so3_fft_b64"] = so3_fft_b64(device, hbm_gbs)
             line["so3_mm_tensor"] = so3_mm_tensor(device, bf16_tf)
+            line["train_step_c4"] = train_step_c4(device)
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist
