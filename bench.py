@@ -356,8 +356,8 @@ def so3_fft_b64(device, hbm_gbs):
 
 
 def so3_mm_tensor(device, bf16_tf):
-    """The spectral product of the widest layer BASELINE's deep model holds (SO3Conv 100 -> 100 at
-    b_out = 10, batch 32): time of so3_mm on the tcgen05 path, algorithmic flops (8 per complex
+    """The spectral product of the widest layer of the deep model among the reference's
+    configurations (SO3Conv 100 -> 100 at b_out = 10, batch 32): time of so3_mm on the tcgen05 path, algorithmic flops (8 per complex
     multiply-add) and the TF32 flops actually issued (three TF32 products per FP32 product),
     against half of the measured bf16 GEMM peak (TF32 runs at half the bf16 rate)."""
     from s2cnn_b200 import so3_mm
