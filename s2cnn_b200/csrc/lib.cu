@@ -649,8 +649,22 @@ static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, in
   void* flag = nullptr;
   S2C_TRY(cuda_check(cudaGetSymbolAddress(&flag, g_tc_err_flag), "tensor-core status flag"));
   p.err = (int*)flag;
-  const long tiles = so3_mm_tc_tiles(op, nl, nb, fi, fo);
-  const bool flush = (long)(2 * nl - 1) * p.nblk > kTcFlushBlocks;   // longest K loop of any degree
+  // Few output tiles (the grad-y product: its rows are only (p, k)) leave most SMs idle: several
+  // CTAs then share a tile, each contracting a slice of the outer index and adding its partial
+  // result atomically into the zeroed output (float additions in arrival order).
+  p.ksplit = 1;
+  {
+    const long plain = so3_mm_tc_tiles(op, nl, nb, fi, fo);
+    if (op == kTcGradY && plain < 100 && nl > 1) p.ksplit = (int)std::min<long>(8, (148 + plain - 1) / plain);
+  }
+  if (p.ksplit > 1) {
+    const size_t out_bytes = (size_t)so3_nspec(nl) * fi * fo * sizeof(float2);
+    S2C_TRY(cuda_check(cudaMemsetAsync(c, 0, out_bytes, st), "so3_mm split-K output clear"));
+  }
+  const long tiles = so3_mm_tc_tiles(op, nl, nb, fi, fo, p.ksplit);
+  // longest K loop of any CTA
+  const long lmax = 2 * nl - 1;
+  const bool flush = ((lmax + p.ksplit - 1) / p.ksplit) * p.nblk > kTcFlushBlocks;
   const bool vec = so3_mm_tc_vec16(op, nb, fi, fo);
 #define S2C_TC_LAUNCH2(OP, FL, NAME)                                                               \
   (vec ? launch_impl(so3_mm_tc_kernel<OP, FL, true>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p)  \

@@ -58,6 +58,8 @@ struct MmTcParams {
   int run;          // floats per outer contraction index: 2 fi (fwd), 2 fo (grad x), 2 nb (grad y)
   int kblk;         // floats per K block (multiple of 8, <= kTcKMax)
   int nblk;         // K blocks per run
+  int ksplit;       // CTAs sharing one output tile (each takes a slice of the outer contraction
+                    // index and adds its partial result atomically into the zeroed output); 1 = none
   int* err;         // device flag, set to 1 on a wait time-out
 };
 
@@ -216,11 +218,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   int l = p.nl - 1;
   long t = blockIdx.x;
   for (;; --l) {
-    const long c = tc_tiles_for(OP, p.nb, p.fi, p.fo, l);
+    const int sl = p.ksplit < 2 * l + 1 ? p.ksplit : 2 * l + 1;
+    const long c = tc_tiles_for(OP, p.nb, p.fi, p.fo, l) * sl;
     if (t < c) break;
     t -= c;
   }
   const int L = 2 * l + 1;
+  // slice of the outer contraction index handled by this CTA
+  const int nsplit = p.ksplit < L ? p.ksplit : L;
+  const int split = (int)(t % nsplit);
+  t /= nsplit;
+  const int o_lo = (int)((long)split * L / nsplit), o_hi = (int)((long)(split + 1) * L / nsplit);
   const TcGeom geo = tc_geom(OP, p.nb, p.fi, p.fo);
   const int RI = geo.RI, CW = geo.CW;
   const int M = L * RI, Np = L * CW;
@@ -260,7 +268,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcBN >> 3) << 17) |
                          ((uint32_t)(kTcBM >> 4) << 24);
 
-  const int nit = L * p.nblk;
+  const int nit = (o_hi - o_lo) * p.nblk;
   bool ok = true;
 
   // Per-thread staging slots.  The (row, 16-byte chunk) handled by a slot and the part of its
@@ -309,8 +317,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   }
 
   auto block_geom = [&](int it, int& oidx, int& k0, int& kvalid) {
-    oidx = it / p.nblk;
-    const int kb = it - oidx * p.nblk;
+    const int oi = it / p.nblk;
+    const int kb = it - oi * p.nblk;
+    oidx = o_lo + oi;
     k0 = kb * p.kblk;
     kvalid = (p.run - k0) < p.kblk ? (p.run - k0) : p.kblk;   // floats with data (even; VEC: multiple of 4)
   };
@@ -484,8 +493,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
             if (gcol < Np) {  // CW is a multiple of 4, so a group of 4 is all in or all out
               const int co = gcol / CW, rem = gcol - co * CW;
               float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
-              *reinterpret_cast<float4*>(dst) =
-                  make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+              if (nsplit > 1) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) atomicAdd(dst + u, v[4 * c4 + u]);
+              } else {
+                *reinterpret_cast<float4*>(dst) =
+                    make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+              }
             }
           }
         } else {
@@ -495,7 +509,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
             if (gcol < Np) {  // one complex number: never straddles an outer column index
               const int co = gcol / CW, rem = gcol - co * CW;
               float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
-              *reinterpret_cast<float2*>(dst) = make_float2(v[2 * c2], v[2 * c2 + 1]);
+              if (nsplit > 1) {
+                atomicAdd(dst, v[2 * c2]);
+                atomicAdd(dst + 1, v[2 * c2 + 1]);
+              } else {
+                *reinterpret_cast<float2*>(dst) = make_float2(v[2 * c2], v[2 * c2 + 1]);
+              }
             }
           }
         }
@@ -523,9 +542,10 @@ inline bool so3_mm_tc_vec16(int op, int nb, int fi, int fo) {
   return (fi % 2 == 0) && (fo % 2 == 0);
 }
 
-inline long so3_mm_tc_tiles(int op, int nl, int nb, int fi, int fo) {
+inline long so3_mm_tc_tiles(int op, int nl, int nb, int fi, int fo, int ksplit = 1) {
   long t = 0;
-  for (int l = 0; l < nl; ++l) t += tc_tiles_for(op, nb, fi, fo, l);
+  for (int l = 0; l < nl; ++l)
+    t += tc_tiles_for(op, nb, fi, fo, l) * (ksplit < 2 * l + 1 ? ksplit : 2 * l + 1);
   return t;
 }
 
