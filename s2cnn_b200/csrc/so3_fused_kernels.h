@@ -91,7 +91,74 @@ struct so3_inv_fused_impl {
       pinfo[pr] = make_int4((int)(p.pan.off[pr] / N), K - lmin, m < 0 ? m + N : m, n);
     }
     // symmetrised half spectrum  Xs = (X[l,m,n] + (-1)^(m-n) conj X[l,-m,-n]) / 2
-    // (four work items per thread at a time so that eight independent row loads are in flight)
+    //
+    // Fast path: one panel row per work item for all ZG batch elements at once.  The block's batch
+    // elements are consecutive, so their spectrum entries are 32 contiguous bytes (two 16-byte
+    // loads); with s2_mm fused they share the batch index i of xs and take consecutive output
+    // features j of ys.  Index arithmetic and the xs loads are then paid once per row, not once
+    // per (row, batch element).
+    const bool prod = p.mode == kS2Product;
+    bool fast = zc == ZG && ZG == 4;
+    if (prod) fast = fast && (p.s2_fout % ZG == 0);
+    else fast = fast && (p.x_zstride % 2 == 0);
+    if (fast) {
+      const int pi = prod ? (int)(z0 / p.s2_fout) : 0, pj = prod ? (int)(z0 - (long)pi * p.s2_fout) : 0;
+      for (int r = ctx.tid; r < p.nrows; r += ctx.nthr) {
+        int l, m, n;
+        rowmap_unpack(p.pan.rowmap[r], l, m, n);
+        float2 av[ZG], bv[ZG];
+        if (prod) {
+          const float2* xa = p.xs + ((long)(l * l + l + m) * p.s2_nb + pi) * p.s2_fin;
+          const float2* xb = p.xs + ((long)(l * l + l - m) * p.s2_nb + pi) * p.s2_fin;
+          const float2* ya = p.ys + (long)(l * l + l + n) * p.s2_fin * p.s2_fout + pj;
+          const float2* yb = p.ys + (long)(l * l + l - n) * p.s2_fin * p.s2_fout + pj;
+#pragma unroll
+          for (int z = 0; z < ZG; ++z) { av[z] = make_float2(0.f, 0.f); bv[z] = make_float2(0.f, 0.f); }
+          for (int k = 0; k < p.s2_fin; ++k) {
+            const float2 xk = xa[k], xm = xb[k];
+            const float4 y01 = *reinterpret_cast<const float4*>(ya + (long)k * p.s2_fout);
+            const float4 y23 = *reinterpret_cast<const float4*>(ya + (long)k * p.s2_fout + 2);
+            const float4 w01 = *reinterpret_cast<const float4*>(yb + (long)k * p.s2_fout);
+            const float4 w23 = *reinterpret_cast<const float4*>(yb + (long)k * p.s2_fout + 2);
+            const float2 yv[ZG] = {make_float2(y01.x, y01.y), make_float2(y01.z, y01.w),
+                                   make_float2(y23.x, y23.y), make_float2(y23.z, y23.w)};
+            const float2 wv[ZG] = {make_float2(w01.x, w01.y), make_float2(w01.z, w01.w),
+                                   make_float2(w23.x, w23.y), make_float2(w23.z, w23.w)};
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) {   // x * conj(y)
+              av[z].x = fmaf(xk.x, yv[z].x, av[z].x);
+              av[z].x = fmaf(xk.y, yv[z].y, av[z].x);
+              av[z].y = fmaf(xk.y, yv[z].x, av[z].y);
+              av[z].y = fmaf(-xk.x, yv[z].y, av[z].y);
+              bv[z].x = fmaf(xm.x, wv[z].x, bv[z].x);
+              bv[z].x = fmaf(xm.y, wv[z].y, bv[z].x);
+              bv[z].y = fmaf(xm.y, wv[z].x, bv[z].y);
+              bv[z].y = fmaf(-xm.x, wv[z].y, bv[z].y);
+            }
+          }
+        } else {
+          const float4* pa = reinterpret_cast<const float4*>(p.x + so3_row(l, m, n) * p.x_zstride + z0);
+          const float4* pb = reinterpret_cast<const float4*>(p.x + so3_row(l, -m, -n) * p.x_zstride + z0);
+          const float4 a01 = pa[0], a23 = pa[1], b01 = pb[0], b23 = pb[1];
+          av[0] = make_float2(a01.x, a01.y); av[1] = make_float2(a01.z, a01.w);
+          av[2] = make_float2(a23.x, a23.y); av[3] = make_float2(a23.z, a23.w);
+          bv[0] = make_float2(b01.x, b01.y); bv[1] = make_float2(b01.z, b01.w);
+          bv[2] = make_float2(b23.x, b23.y); bv[3] = make_float2(b23.z, b23.w);
+        }
+        const float fudge = ((m - n) & 1) ? -1.f : 1.f;
+#pragma unroll
+        for (int z = 0; z < ZG; ++z) {
+          float2 a = av[z], b = bv[z];
+          if (p.mode == kSo3RotI) {
+            a = make_float2(a.y, -a.x);
+            b = make_float2(b.y, -b.x);
+          }
+          Xh[r * ZG + z] = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
+        }
+      }
+    } else {
+    // general path: one (row, batch element) per work item, four at a time so that eight
+    // independent row loads are in flight
     for (int base = ctx.tid; base < p.nrows * ZG; base += 4 * ctx.nthr) {
       int packed[4];
       float2 a[4], b[4];
@@ -134,6 +201,7 @@ struct so3_inv_fused_impl {
         const float fudge = ((m - n) & 1) ? -1.f : 1.f;
         Xh[it] = make_float2(0.5f * (av.x + fudge * bv.x), 0.5f * (av.y - fudge * bv.y));
       }
+    }
     }
     ctx.sync();
 
