@@ -71,11 +71,11 @@ def make_net(device, seed=0):
             self.linear = torch.nn.Linear(NET["f2"], NET["nclass"])
 
         def forward(self, x):
-            # relu(conv1) -> conv2 -> relu -> integrate -> linear, with each ReLU applied by its
-            # consumer while it reads the pre-activation tensor (same values, two passes less)
+            # relu(conv1) -> conv2 -> relu -> integrate -> linear: the first ReLU is applied by conv2
+            # while it reads the pre-activation tensor, the second ReLU and the integration by the
+            # last pass of conv2's synthesis (same values; conv2's output signal is never written)
             x = self.conv1(x)
-            x = self.conv2(x, relu_input=True)
-            x = S.so3_relu_integrate(x)
+            x = self.conv2(x, relu_input=True, relu_integrate=True)   # [batch, f2]
             return self.linear(x)
 
     return Net().to(device).eval()
@@ -107,7 +107,6 @@ def kernel_bytes(B):
     b0, b1, b2, f0, f1, f2 = (NET[k] for k in ("b0", "b1", "b2", "f0", "f1", "f2"))
     c = 8  # bytes per complex
     sig1 = B * f1 * (2 * b1) ** 3 * 4   # conv1 output / conv2 input signal
-    sig2 = B * f2 * (2 * b2) ** 3 * 4   # conv2 output signal
     out = {}
     # S2 analysis of the real input in one kernel: reads the signal, writes the S2 spectrum
     N0 = 2 * b0
@@ -116,11 +115,13 @@ def kernel_bytes(B):
     out["rft_forward"] = (f0 * f1 * 24 * 4 + b1 * b1 * f0 * f1 * c) + (f1 * f2 * 192 * 4 + n3(b2) * f1 * f2 * c)
     # conv1: s2_mm fused into the synthesis (reads the two S2 spectra, writes the signal)
     # conv2 synthesis: reads the SO(3) spectrum, writes the signal
-    out["so3_inv_fused"] = (b1 * b1 * (B * f0 + f0 * f1) * c + sig1) + (n3(b2) * B * f2 * c + sig2)
+    # (its ReLU + integration tail is fused in: conv2's output signal is not written, one float
+    # per batch element and feature is)
+    out["so3_inv_fused<%d>" % (2 * b1)] = b1 * b1 * (B * f0 + f0 * f1) * c + sig1
+    out["so3_inv_fused<%d>" % (2 * b2)] = n3(b2) * B * f2 * c + B * f2 * 4
     # conv2 analysis (ReLU on load): reads the signal, writes the spectrum
-    out["so3_fwd_fused"] = sig1 + n3(b2) * B * f1 * c
+    out["so3_fwd_fused<%d>" % (2 * b1)] = sig1 + n3(b2) * B * f1 * c
     out["so3_mm_tc_kernel"] = n3(b2) * (B * f1 + f1 * f2 + B * f2) * c
-    out["so3_integrate_fwd"] = sig2 + B * f2 * 4
     return out
 
 
@@ -584,8 +585,8 @@ def run_ours(args):
         # DRAM bytes per step of this kernel's launches from one ncu capture of this same command
         # (profiles/net_b30_10_6_launch_list.md); below the algorithmic bytes because part of the
         # output is still in L2 when the kernel ends - no re-reads
-        traffic = {"so3_inv_fused": 1.5e6 + 104.7e6 + 23.5e6 + 9.6e6,
-                   "so3_fwd_fused": 163.9e6 + 3.8e6}.get(top["kernel"]) if B == 256 else None
+        traffic = {"so3_inv_fused<20>": 1.5e6 + 104.7e6,
+                   "so3_fwd_fused<20>": 163.9e6 + 3.8e6}.get(top["kernel"]) if B == 256 else None
         roofline = {"kernel": top["kernel"], "bound": "hbm", "achieved": ach, "peak": hbm_gbs,
                     "unit": "GB/s", "frac": ach / hbm_gbs, "traffic": traffic,
                     "peak_source": peak_kind,
@@ -604,7 +605,7 @@ def run_ours(args):
         "config": {"workload": "net_b30_10_6", "batch_per_gpu": B, "global_batch": B * world,
                    "layers": "S2Conv(1->20,b30->10) ReLU SO3Conv(20->40,b10->6) ReLU "
                              "so3_integrate Linear(40->10)",
-                   "fusion": "ReLUs applied on load by the next op; s2_mm inside the synthesis kernel",
+                   "fusion": "first ReLU applied on load by conv2; s2_mm inside conv1's synthesis kernel; second ReLU and so3_integrate inside conv2's synthesis kernel",
                    "launch": "eager" if args.no_graph else "CUDA graph replay (s2cnn_b200.graph.GraphedForward)",
                    "sharding": "batch over ranks, no collective in forward",
                    "l2": "256 MB flush write between timed steps"},

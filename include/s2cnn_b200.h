@@ -100,6 +100,13 @@ int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, in
 int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                   const float* bias, int nfeature, void* workspace, size_t workspace_bytes,
                   void* stream);
+/* so3_integrate(relu(so3_rifft(x) + bias)) without writing the signal: out [nbatch] - the tail
+ * "SO3Convolution -> ReLU -> so3_integrate" of the reference's classifiers (e.g.
+ * examples/mnist/run.py:88-97) in the synthesis kernel.  Only for 2 b_out <= 32 (single-kernel
+ * path); other sizes return "unsupported".  Replaces so3_rifft (s2cnn/soft/so3_fft.py:158-202)
+ * followed by so3_integrate (s2cnn/soft/so3_integrate.py:7-29). */
+int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_in, int b_out,
+                                 const float* bias, int nfeature, void* stream);
 /* Same result as s2c_so3_rifft, for callers that cannot obtain device memory at call time (a
  * process whose GPU memory is wholly pre-reserved by another allocator, or a loop that must avoid
  * the device-wide synchronisation of cudaMalloc/cudaFree): no workspace argument and no device

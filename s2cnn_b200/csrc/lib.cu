@@ -185,7 +185,7 @@ static bool so3_synthesis_is_fused(int b_in, int b_out) {
 static int so3_synthesis(const float2* x, float* out, long out_stride, long out_off, long nbatch,
                          int b_in, int b_out, bool weighted, int mode, const float* bias,
                          int nfeat, void* ws, size_t ws_bytes, stream_t st,
-                         const S2ProductArgs* prod = nullptr) {
+                         const S2ProductArgs* prod = nullptr, float* integral = nullptr) {
   const int N = 2 * b_out, K = std::min(b_in, b_out);
   FftDev fft;
   PanelsDev pan;
@@ -201,6 +201,13 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N); f.PS = fused_plane_stride(N, K);
     f.nrows = pan.nrows; f.mode = mode;
     f.xs = nullptr; f.ys = nullptr; f.s2_nb = f.s2_fin = f.s2_fout = 0;
+    f.iw = nullptr; f.isum = nullptr;
+    if (integral) {
+      if (N % f.BG != 0 || kFusedZG * f.BG * (N / 2) > 256)
+        return fail(S2C_ERR_UNSUPPORTED, "fused integration: unsupported grouping");
+      S2C_TRY(TableCache::get().quad_weights(b_out, &f.iw));
+      f.isum = integral;
+    }
     if (prod) {
       f.mode = kS2Product;
       f.xs = prod->xs; f.ys = prod->ys;
@@ -212,6 +219,8 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
                                         fused_smem_bytes(N, pan.nrows), st, f));
     return rc;
   }
+  if (integral)
+    return fail(S2C_ERR_UNSUPPORTED, "fused ReLU + integration needs the small-bandwidth path");
   const size_t per_z = so3_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || ws == nullptr)
@@ -492,6 +501,19 @@ int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, 
   if (bias && nfeature < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft: nfeature must be >= 1 with a bias");
   return so3_synthesis((const float2*)x, out, 1, 0, nbatch, b_in, b_out, for_grad != 0, kSo3Real,
                        bias, nfeature, ws, ws_bytes, as_stream(stream));
+}
+
+int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_in, int b_out,
+                                 const float* bias, int nfeature, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || nbatch < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_relu_integrate: bad argument");
+  if (bias && nfeature < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_relu_integrate: nfeature must be >= 1 with a bias");
+  if (!so3_synthesis_is_fused(b_in, b_out))
+    return fail(S2C_ERR_UNSUPPORTED, "s2c_so3_rifft_relu_integrate: needs 2 b_out <= 32");
+  return so3_synthesis((const float2*)x, nullptr, 1, 0, nbatch, b_in, b_out, false, kSo3Real, bias,
+                       nfeature, nullptr, 0, as_stream(stream), nullptr, out);
 }
 
 size_t s2c_s2_conv_synthesis_workspace(int nbatch, int f_out, int b) {

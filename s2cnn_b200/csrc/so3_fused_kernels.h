@@ -15,6 +15,9 @@
 // (s2cnn/soft/so3_fft.py:64-112,158-202,246-443) and produce the same values.
 #pragma once
 
+#include <map>
+#include <mutex>
+#include <string>
 #include <type_traits>
 
 #include "backend.h"
@@ -47,6 +50,10 @@ struct InvFusedParams {
   const float2* xs;    // [K*K, s2_nb, s2_fin]
   const float2* ys;    // [K*K, s2_fin, s2_fout]
   int s2_nb, s2_fin, s2_fout;
+  // optional tail of a network: instead of writing the signal, integrate max(signal, 0) over SO(3)
+  // (so3_integrate(relu(.)), s2cnn/soft/so3_integrate.py:7-29) and write one number per batch element
+  const float* iw;     // quadrature weights [N] (null: write the signal)
+  float* isum;         // [nbatch]
 };
 
 S2C_D float2 s2_product_entry(const InvFusedParams& p, int l, int m, int n, int i, int j) {
@@ -205,6 +212,7 @@ struct so3_inv_fused_impl {
     }
     ctx.sync();
 
+    float ipart = 0.f;   // this thread's share of the integral (its rows of every beta group)
     for (int bg0 = 0; bg0 < N; bg0 += p.BG) {
       const int bc = (N - bg0) < p.BG ? (N - bg0) : p.BG;
       // ---- Wigner contraction over l: one (pair, beta) per work item, ZG accumulators.  The
@@ -287,6 +295,16 @@ struct so3_inv_fused_impl {
         fft_reg<N, +1>(v, tw);
         float add = 0.f;
         if (p.bias) add = p.bias[(z0 + z) % p.nfeat];
+        if (p.iw) {
+          // the signal is not written: max(x, 0) of both rows, summed over gamma, times w_beta
+          float rs = 0.f;
+#pragma unroll
+          for (int g = 0; g < N; ++g) {
+            const float a1 = v[g].x + add, a2 = v[g].y + add;
+            rs += (a1 > 0.f ? a1 : 0.f) + (a2 > 0.f ? a2 : 0.f);
+          }
+          ipart = fmaf(p.iw[bg0 + bi], rs, ipart);
+        } else
         // store the two finished rows straight from registers (the plane is contiguous in memory)
         if (z < zc) {
           const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;   // first float of row ap
@@ -318,6 +336,20 @@ struct so3_inv_fused_impl {
         }
       }
       ctx.sync();
+    }
+    if (p.iw) {
+      // Every group has the same number of betas here (the host only asks for the integral when BG
+      // divides N and one pass of the block covers a group), so thread t always served batch
+      // element t / (BG * N/2): sum the threads of each element in a fixed order.
+      float* red = reinterpret_cast<float*>(planes);
+      red[ctx.tid] = ipart;
+      ctx.sync();
+      if (ctx.tid < zc) {
+        const int per = p.BG * (N / 2);
+        float sum = 0.f;
+        for (int t = 0; t < per; ++t) sum += red[ctx.tid * per + t];
+        p.isum[z0 + ctx.tid] = sum;
+      }
     }
   }
 };
@@ -489,8 +521,21 @@ __global__ void __launch_bounds__(256) so3_fwd_fused(const FwdFusedParams p) {
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
   so3_fwd_fused_impl<N>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
-#define S2C_LAUNCH_N(name, N, grid, block, smem, stream, params) \
-  s2c::launch_impl(name<N>, #name, (long)(grid), (int)(block), (size_t)(smem), stream, params)
+// name of an instantiation for the launch records, e.g. "so3_inv_fused<20>" (interned: the
+// records keep the pointer)
+inline const char* kernel_name_n(const char* base, int n) {
+  static std::mutex mu;
+  static std::map<std::pair<std::string, int>, std::string> names;
+  std::lock_guard<std::mutex> g(mu);
+  auto key = std::make_pair(std::string(base), n);
+  auto it = names.find(key);
+  if (it == names.end())
+    it = names.emplace(key, std::string(base) + "<" + std::to_string(n) + ">").first;
+  return it->second.c_str();
+}
+#define S2C_LAUNCH_N(name, N, grid, block, smem, stream, params)                              \
+  s2c::launch_impl(name<N>, s2c::kernel_name_n(#name, N), (long)(grid), (int)(block),          \
+                   (size_t)(smem), stream, params)
 #else
 #define S2C_LAUNCH_N(name, N, grid, block, smem, stream, params) \
   s2c::emu_launch<name##_impl<N>>(#name, (long)(grid), (int)(block), (size_t)(smem), params)

@@ -121,6 +121,29 @@ class Ops:
                           self._stream(x))
         return out.view(*lead, n, n, n)
 
+    def so3_rifft_relu_integrate(self, x, bias=None, b_out=None):
+        """so3_integrate(relu(so3_rifft(x) + bias)) in one kernel, the signal never written:
+        [nspec(b_in), ..., 2] -> [...].  Only 2 b_out <= 32."""
+        self._prep(x, bias)
+        assert x.size(-1) == 2
+        b_in = bandwidth_from_so3_nspec(x.size(0))
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[1:-1])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        out = x.new_empty((nbatch,))
+        nfeat = 0
+        bias_ptr = None
+        if bias is not None:
+            bias = bias.contiguous().view(-1)
+            nfeat = bias.numel()
+            assert len(lead) >= 1 and lead[-1] == nfeat, (lead, nfeat)
+            bias_ptr = bias.data_ptr()
+        with self._ctx(x):
+            self.lib.call("s2c_so3_rifft_relu_integrate", x.data_ptr(), out.data_ptr(), nbatch,
+                          b_in, b_out, bias_ptr, nfeat, self._stream(x))
+        return out.view(*lead)
+
     def s2_conv_synthesis(self, xs, ys, bias=None):
         """so3_rifft(s2_mm(xs, ys)) + bias without materialising the SO(3) spectrum (small b).
         xs [b^2, batch, f_in, 2], ys [b^2, f_in, f_out, 2] -> [batch, f_out, 2b, 2b, 2b]"""

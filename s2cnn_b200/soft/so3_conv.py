@@ -6,9 +6,11 @@ import torch
 from torch.nn.modules import Module
 from torch.nn.parameter import Parameter
 
+from ..ops import cuda_ops
 from ..so3_ft import so3_rft
 from ..so3_mm import so3_mm
 from .so3_fft import SO3_fft_real, SO3_fft_real_relu, SO3_ifft_real_bias
+from .so3_integrate import so3_relu_integrate
 
 
 class SO3Convolution(Module):
@@ -31,10 +33,12 @@ class SO3Convolution(Module):
         # the scaling stays outside the parameter (so3_conv.py:30-34)
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
 
-    def forward(self, x, relu_input=False):  # pylint: disable=W
+    def forward(self, x, relu_input=False, relu_integrate=False):  # pylint: disable=W
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
         :relu_input: (extension) compute conv(relu(x)); the activation is applied while x is read
+        :relu_integrate: (extension) return so3_integrate(relu(conv(x))) [batch, feature_out]; without
+                         autograd and for 2 b_out <= 32 the output signal is never written
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
         assert x.size(1) == self.nfeature_in
@@ -51,6 +55,10 @@ class SO3Convolution(Module):
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)
         z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
+        if relu_integrate:
+            if 2 * self.b_out <= 32 and not (torch.is_grad_enabled() and (z.requires_grad or self.bias.requires_grad)):
+                return cuda_ops().so3_rifft_relu_integrate(z, bias=self.bias)  # [batch, feature_out]
+            return so3_relu_integrate(SO3_ifft_real_bias.apply(z, self.bias))
         return SO3_ifft_real_bias.apply(z, self.bias)  # [batch, feature_out, beta, alpha, gamma]
 
 

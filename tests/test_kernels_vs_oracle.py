@@ -311,6 +311,23 @@ def test_rfft_with_relu_on_load(backend):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,lead", [(6, 6, (5, 3)), (4, 7, (2, 2)), (5, 3, (7,)), (10, 10, (1, 2))])
+def test_synthesis_relu_integrate_fused(backend, b_in, b_out, lead):
+    """so3_integrate(relu(so3_rifft(x) + bias)) in the synthesis kernel (the signal is never
+    written), incl. a batch count that leaves a partial block."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in * 7 + b_out)
+    s = torch.randn(n3(b_in), *lead, 2, generator=gen)
+    bias = torch.randn(lead[-1], generator=gen)
+    shape = (1,) * (len(lead) - 1) + (lead[-1], 1, 1, 1)
+    ref = O.so3_integrate(torch.relu(O.so3_rifft(s, b_out=b_out) + bias.view(shape)))
+    got = ops.so3_rifft_relu_integrate(s.to(dev), bias=bias.to(dev), b_out=b_out)
+    assert_close(got, ref, "rifft + relu + integrate")
+    ref0 = O.so3_integrate(torch.relu(O.so3_rifft(s, b_out=b_out)))
+    assert_close(ops.so3_rifft_relu_integrate(s.to(dev), b_out=b_out), ref0, "no bias")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b,nb,fi,fo", [(4, 3, 2, 3), (6, 5, 1, 4), (1, 2, 3, 2), (10, 2, 1, 6)])
 def test_s2_product_synthesis_fused(backend, b, nb, fi, fo):
     """so3_rifft(s2_mm(x, y)) + bias in one call, single-kernel path and general path."""
