@@ -107,6 +107,14 @@ int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, 
  * followed by so3_integrate (s2cnn/soft/so3_integrate.py:7-29). */
 int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_in, int b_out,
                                  const float* bias, int nfeature, void* stream);
+/* Two layers' transforms in one kernel, the signal between them never written:
+ *   out = so3_rfft(relu(so3_rifft(s2_mm(xs, ys)) + bias), b_out = b_next)
+ * xs [b*b, nbatch, f_in, 2], ys [b*b, f_in, f_out, 2], bias [f_out] or NULL,
+ * out [nspec(b_next), nbatch, f_out, 2].  Only for 2 b <= 32 and b_next <= b; other sizes return
+ * "unsupported".  Replaces the tail of S2Convolution.forward (s2cnn/soft/s2_conv.py:42-45), the ReLU
+ * and the head of the next SO3Convolution.forward (s2cnn/soft/so3_conv.py:50). */
+int s2c_s2_conv_relu_so3_rfft(const float* xs, const float* ys, float* out, int nbatch, int f_in,
+                              int f_out, int b, int b_next, const float* bias, void* stream);
 /* Same result as s2c_so3_rifft, for callers that cannot obtain device memory at call time (a
  * process whose GPU memory is wholly pre-reserved by another allocator, or a loop that must avoid
  * the device-wide synchronisation of cudaMalloc/cudaFree): no workspace argument and no device

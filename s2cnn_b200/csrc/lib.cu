@@ -14,6 +14,7 @@
 #include "so3_plane_kernels.h"
 #include "s2_fused_kernels.h"
 #include "so3_fused_kernels.h"
+#include "so3_relay_kernels.h"
 #include "wigner_tiled.h"
 #include "cgemm_kernels.h"
 #include "s2_mm_thin.h"
@@ -514,6 +515,49 @@ int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_
     return fail(S2C_ERR_UNSUPPORTED, "s2c_so3_rifft_relu_integrate: needs 2 b_out <= 32");
   return so3_synthesis((const float2*)x, nullptr, 1, 0, nbatch, b_in, b_out, false, kSo3Real, bias,
                        nfeature, nullptr, 0, as_stream(stream), nullptr, out);
+}
+
+// Largest beta group (a divisor of N whose row stage fits one pass of the block) that keeps three
+// blocks of the relay kernel on an SM; failing that, the largest that fits at all (0: none).
+static int relay_bg(int N, int Kin, int nrows_in, int nrows_out) {
+  int best3 = 0, best = 0;
+  for (int d = 1; d <= N && d <= kMaxBG; ++d) {
+    if (N % d != 0 || kFusedZG * d * (N / 2) > 256) continue;
+    const size_t sm = relay_smem_bytes(N, Kin, nrows_in, nrows_out, d);
+    if (sm <= (size_t)dev_smem_limit() - 1024) best = d;
+    if (3 * (sm + 1024) <= (size_t)227 * 1024) best3 = d;
+  }
+  return best3 ? best3 : best;
+}
+
+int s2c_s2_conv_relu_so3_rfft(const float* xs, const float* ys, float* out, int nbatch, int f_in,
+                              int f_out, int b, int b_next, const float* bias, void* stream) {
+  S2C_TRY(check_b(b, b_next));
+  if (!xs || !ys || !out || nbatch < 1 || f_in < 1 || f_out < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_s2_conv_relu_so3_rfft: bad argument");
+  const int N = 2 * b;
+  if (N > kFusedMaxN || b_next > b)
+    return fail(S2C_ERR_UNSUPPORTED, "s2c_s2_conv_relu_so3_rfft: needs 2 b <= 32 and b_next <= b");
+  FftDev fft;
+  RelayParams f;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b, b, b, false, false, f.pin));
+  S2C_TRY(TableCache::get().panels(b, b_next, b_next, true, false, f.pout));
+  f.BG = relay_bg(N, b, f.pin.nrows, f.pout.nrows);
+  if (f.BG < 1) return fail(S2C_ERR_UNSUPPORTED, "s2c_s2_conv_relu_so3_rfft: shared memory");
+  S2C_TRY(TableCache::get().grouped(b, b, b, false, f.BG, &f.win_g, &f.win_stride));
+  f.xs = (const float2*)xs; f.ys = (const float2*)ys;
+  f.s2_nb = nbatch; f.s2_fin = f_in; f.s2_fout = f_out;
+  f.bias = bias; f.nfeat = f_out;
+  f.out = (float2*)out; f.out_zstride = (long)nbatch * f_out;
+  f.tw = fft.tw;
+  f.nbatch = nbatch * f_out; f.Kin = b; f.Kout = b_next;
+  f.KP = fused_kp(N); f.PS = fused_plane_stride(N, b);
+  int rc = S2C_OK;
+  const long grid = ((long)f.nbatch + kFusedZG - 1) / kFusedZG;
+  const size_t sm = relay_smem_bytes(N, b, f.pin.nrows, f.pout.nrows, f.BG);
+  S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_relay_fused, kN, grid, 256, sm, as_stream(stream), f));
+  return rc;
 }
 
 size_t s2c_s2_conv_synthesis_workspace(int nbatch, int f_out, int b) {

@@ -211,6 +211,37 @@ class TableCache {
     return S2C_OK;
   }
 
+  // SO(3) panel values regrouped for beta groups of `bg` (layout of PanelsDev::data_g), for kernels
+  // that walk the beta axis in groups other than fused_bg(2 b_beta).  stride = floats per group.
+  int grouped(int b_beta, int nl, int K, bool weighted, int bg, const float** data_g, int* stride) {
+    std::lock_guard<std::mutex> g(mu_);
+    const int dev = dev_current();
+    auto key = std::make_tuple(dev, b_beta, nl, K, (int)weighted, bg);
+    auto it = grouped_.find(key);
+    if (it == grouped_.end()) {
+      const int nbeta = 2 * b_beta;
+      if (bg < 1 || nbeta % bg != 0) return fail(S2C_ERR_BAD_ARG, "grouped table: bad group size");
+      std::vector<float> data;
+      std::vector<long long> off;
+      build_panels(b_beta, nl, K, weighted, false, data, off);
+      const int nrows = (int)(off.back() / nbeta);
+      const int st = (nrows * bg + 3) / 4 * 4;
+      std::vector<float> grouped((size_t)st * (nbeta / bg), 0.f);
+      for (int gidx = 0; gidx < nbeta / bg; ++gidx)
+        for (int r = 0; r < nrows; ++r)
+          for (int bi = 0; bi < bg; ++bi)
+            grouped[(size_t)gidx * st + (size_t)r * bg + bi] = data[(size_t)r * nbeta + gidx * bg + bi];
+      void* dg = dev_alloc(grouped.size() * sizeof(float));
+      if (!dg) return fail(S2C_ERR_CUDA, "table allocation failed");
+      const int rc = dev_upload(dg, grouped.data(), grouped.size() * sizeof(float));
+      if (rc) return rc;
+      it = grouped_.emplace(key, std::make_pair((const float*)dg, st)).first;
+    }
+    *data_g = it->second.first;
+    *stride = it->second.second;
+    return S2C_OK;
+  }
+
   int quad_weights(int b, const float** out) {
     std::lock_guard<std::mutex> g(mu_);
     const int dev = dev_current();
@@ -240,6 +271,8 @@ class TableCache {
       if (kv.second.data_g) dev_free((void*)kv.second.data_g);
     }
     for (auto& kv : quad_) dev_free((void*)kv.second);
+    for (auto& kv : grouped_) dev_free((void*)kv.second.first);
+    grouped_.clear();
     fft_.clear();
     panels_.clear();
     quad_.clear();
@@ -250,6 +283,7 @@ class TableCache {
   std::map<std::pair<int, int>, FftDev> fft_;
   std::map<std::tuple<int, int, int, int, int, int>, PanelsDev> panels_;
   std::map<std::pair<int, int>, const float*> quad_;
+  std::map<std::tuple<int, int, int, int, int, int>, std::pair<const float*, int>> grouped_;
 };
 
 }  // namespace s2c

@@ -144,6 +144,26 @@ class Ops:
                           b_in, b_out, bias_ptr, nfeat, self._stream(x))
         return out.view(*lead)
 
+    def s2_conv_relu_so3_rfft(self, xs, ys, bias, b_next):
+        """so3_rfft(relu(so3_rifft(s2_mm(xs, ys)) + bias), b_out=b_next) in one kernel (small b).
+        xs [b^2, batch, f_in, 2], ys [b^2, f_in, f_out, 2] -> [nspec(b_next), batch, f_out, 2]"""
+        self._prep(xs, ys, bias)
+        nspec, nbatch, f_in, two = xs.shape
+        b = int(round(nspec ** 0.5))
+        assert b * b == nspec and two == 2 and tuple(ys.shape[:2]) == (nspec, f_in)
+        f_out = ys.size(2)
+        xs, ys = xs.contiguous(), ys.contiguous()
+        bias_ptr = None
+        if bias is not None:
+            bias = bias.contiguous().view(-1)
+            assert bias.numel() == f_out
+            bias_ptr = bias.data_ptr()
+        out = xs.new_empty((so3_nspec(b_next), nbatch, f_out, 2))
+        with self._ctx(xs):
+            self.lib.call("s2c_s2_conv_relu_so3_rfft", xs.data_ptr(), ys.data_ptr(), out.data_ptr(),
+                          nbatch, f_in, f_out, b, b_next, bias_ptr, self._stream(xs))
+        return out
+
     def s2_conv_synthesis(self, xs, ys, bias=None):
         """so3_rifft(s2_mm(xs, ys)) + bias without materialising the SO(3) spectrum (small b).
         xs [b^2, batch, f_in, 2], ys [b^2, f_in, f_out, 2] -> [batch, f_out, 2b, 2b, 2b]"""

@@ -8,7 +8,7 @@ from torch.nn.parameter import Parameter
 from ..ops import cuda_ops
 from ..s2_ft import s2_rft
 from .s2_fft import S2_fft_real
-from .so3_fft import so3_rfft
+from .so3_fft import so3_rfft, SO3_fft_real
 
 
 class _S2ProductSynthesis(torch.autograd.Function):
@@ -60,15 +60,26 @@ class S2Convolution(Module):
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 4.) / (self.b_in ** 2.))
         self.bias = Parameter(torch.zeros(1, nfeature_out, 1, 1, 1))
 
-    def forward(self, x):  # pylint: disable=W
+    def forward(self, x, relu_so3_fft=None):  # pylint: disable=W
         '''
         :x:      [batch, feature_in,  beta, alpha]
+        :relu_so3_fft: (extension) bandwidth b_next of the SO3Convolution that follows: return
+                 SO3_fft_real(relu(conv(x)), b_next) - that layer's input spectrum
+                 [l * m * n, batch, feature_out, complex] (pass it on with ``input_spectrum=True``).
+                 Without autograd and for 2 b_out <= 32 the signal between the layers is never written.
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
         assert x.size(1) == self.nfeature_in
         assert x.size(2) == 2 * self.b_in
         assert x.size(3) == 2 * self.b_in
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.kernel.requires_grad or
+                                                  self.bias.requires_grad)
         x = S2_fft_real.apply(x, self.b_out)  # [l * m, batch, feature_in, complex]
         y = s2_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m, feature_in, feature_out, complex]
+        if relu_so3_fft is not None:
+            b_next = int(relu_so3_fft)
+            if not needs_grad and 2 * self.b_out <= 32 and b_next <= self.b_out:
+                return cuda_ops().s2_conv_relu_so3_rfft(x, y, self.bias, b_next)
+            return SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(x, y, self.bias)), b_next)
         # s2_mm -> SO3_ifft_real -> + bias, fused: [batch, feature_out, beta, alpha, gamma]
         return _S2ProductSynthesis.apply(x, y, self.bias)

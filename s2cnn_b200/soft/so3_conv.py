@@ -33,24 +33,29 @@ class SO3Convolution(Module):
         # the scaling stays outside the parameter (so3_conv.py:30-34)
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
 
-    def forward(self, x, relu_input=False, relu_integrate=False):  # pylint: disable=W
+    def forward(self, x, relu_input=False, relu_integrate=False, input_spectrum=False):  # pylint: disable=W
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
+        :input_spectrum: (extension) x is already SO3_fft_real(signal, b_out), as returned by
+                         ``S2Convolution.forward(..., relu_so3_fft=b_out)``
         :relu_input: (extension) compute conv(relu(x)); the activation is applied while x is read
         :relu_integrate: (extension) return so3_integrate(relu(conv(x))) [batch, feature_out]; without
                          autograd and for 2 b_out <= 32 the output signal is never written
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
-        assert x.size(1) == self.nfeature_in
-        assert x.size(2) == 2 * self.b_in
-        assert x.size(3) == 2 * self.b_in
-        assert x.size(4) == 2 * self.b_in
-        if relu_input and 2 * self.b_in <= 32:
-            x = SO3_fft_real_relu.apply(x, self.b_out)
+        if input_spectrum:
+            assert x.dim() == 4 and x.size(2) == self.nfeature_in and x.size(3) == 2
         else:
-            if relu_input:
-                x = torch.relu(x)
-            x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
+            assert x.size(1) == self.nfeature_in
+            assert x.size(2) == 2 * self.b_in
+            assert x.size(3) == 2 * self.b_in
+            assert x.size(4) == 2 * self.b_in
+            if relu_input and 2 * self.b_in <= 32:
+                x = SO3_fft_real_relu.apply(x, self.b_out)
+            else:
+                if relu_input:
+                    x = torch.relu(x)
+                x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
         y = so3_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m * n, feature_in, feature_out, complex]
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)

@@ -83,6 +83,8 @@ def test_config3_network_forward_fused_activations():
         plain = lin(S.so3_integrate(torch.relu(c2(torch.relu(c1(xd))))))
         fused = lin(S.so3_relu_integrate(c2(c1(xd), relu_input=True)))
         tail = lin(c2(c1(xd), relu_input=True, relu_integrate=True))
+        relay = lin(c2(c1(xd, relu_so3_fft=c2.b_out), input_spectrum=True, relu_integrate=True))
     assert_close(plain, ref, "config 3 logits, separate ReLUs")
     assert_close(fused, ref, "config 3 logits, ReLUs applied on load")
     assert_close(tail, ref, "config 3 logits, ReLU + integration inside the synthesis")
+    assert_close(relay, ref, "config 3 logits, both layers' transforms in one kernel")

@@ -328,6 +328,25 @@ def test_synthesis_relu_integrate_fused(backend, b_in, b_out, lead):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b,b_next,nb,fi,fo", [(4, 3, 3, 2, 3), (6, 6, 5, 1, 4), (10, 6, 2, 1, 6),
+                                               (5, 2, 1, 3, 2)])
+def test_two_layer_relay_kernel(backend, b, b_next, nb, fi, fo):
+    """so3_rfft(relu(so3_rifft(s2_mm(xs, ys)) + bias), b_next) in one kernel against the same chain
+    through the oracle."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b * 13 + b_next)
+    xs = torch.randn(b * b, nb, fi, 2, generator=gen)
+    ys = torch.randn(b * b, fi, fo, 2, generator=gen)
+    bias = torch.randn(fo, generator=gen)
+    z = O.so3_rifft(O.s2_mm(xs, ys)) + bias.view(1, fo, 1, 1, 1)
+    ref = O.so3_rfft(torch.relu(z), b_out=b_next)
+    got = ops.s2_conv_relu_so3_rfft(xs.to(dev), ys.to(dev), bias.to(dev), b_next)
+    assert_close(got, ref, "relay")
+    ref0 = O.so3_rfft(torch.relu(O.so3_rifft(O.s2_mm(xs, ys))), b_out=b_next)
+    assert_close(ops.s2_conv_relu_so3_rfft(xs.to(dev), ys.to(dev), None, b_next), ref0, "relay, no bias")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b,nb,fi,fo", [(4, 3, 2, 3), (6, 5, 1, 4), (1, 2, 3, 2), (10, 2, 1, 6)])
 def test_s2_product_synthesis_fused(backend, b, nb, fi, fo):
     """so3_rifft(s2_mm(x, y)) + bias in one call, single-kernel path and general path."""
