@@ -586,9 +586,10 @@ def run_ours(args):
     else:
         ach = top["GBps"]
         # DRAM bytes per step of this kernel's launches from one ncu capture of this same command
-        # (profiles/net_b30_10_6_launch_list.md); below the algorithmic bytes because part of the
-        # output is still in L2 when the kernel ends - no re-reads
-        traffic = {"so3_inv_fused<20>": 1.5e6 + 104.7e6,
+        # (profiles/net_b30_10_6_launch_list.md); far below the algorithmic bytes for the fused
+        # kernels, which keep the tensors at the module boundaries on chip
+        traffic = {"so3_relay_fused<20>": 9.0e6 + 0.02e6, "so3_inv_fused<12>": 23.5e6,
+                   "so3_inv_fused<20>": 1.5e6 + 104.7e6,
                    "so3_fwd_fused<20>": 163.9e6 + 3.8e6}.get(top["kernel"]) if B == 256 else None
         roofline = {"kernel": top["kernel"], "bound": "hbm", "achieved": ach, "peak": hbm_gbs,
                     "unit": "GB/s", "frac": ach / hbm_gbs, "traffic": traffic,
