@@ -201,3 +201,36 @@ def test_fused_relu_variants_match_unfused(backend):
         assert_close(ya, yb.detach(), "fused relu fwd")
         assert_close(ga, xb.grad, "fused relu gx")
         assert_close(gka, conv.kernel.grad, "fused relu gk")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_fused_network_paths_match_plain_modules(backend):
+    """The inference-only extensions of the modules - ReLU applied on load, the two-layer relay
+    (S2Convolution tail + ReLU + SO3Convolution head in one kernel) and ReLU + so3_integrate inside
+    the last synthesis - give the same values as the plain chain of modules; with autograd enabled
+    the same keyword arguments fall back to that chain."""
+    import s2cnn_b200 as S
+    g2 = S.s2_near_identity_grid(max_beta=np.pi / 16, n_alpha=6, n_beta=2)
+    g3 = S.so3_near_identity_grid(max_beta=np.pi / 8, n_alpha=4, n_beta=2, n_gamma=2)
+    torch.manual_seed(21)
+    with backends.active(backend) as (_, dev):
+        c1 = S.S2Convolution(2, 4, 8, 5, g2).to(dev)
+        c2 = S.SO3Convolution(4, 3, 5, 3, g3).to(dev)
+        with torch.no_grad():
+            c1.bias.copy_(torch.randn(c1.bias.shape))
+            c2.bias.copy_(torch.randn(c2.bias.shape))
+        x = torch.randn(3, 2, 16, 16).to(dev)
+        with torch.no_grad():
+            plain = S.so3_integrate(torch.relu(c2(torch.relu(c1(x)))))
+            on_load = S.so3_relu_integrate(c2(c1(x), relu_input=True))
+            tail = c2(c1(x), relu_input=True, relu_integrate=True)
+            relay = c2(c1(x, relu_so3_fft=c2.b_out), input_spectrum=True, relu_integrate=True)
+        for name, got in (("relu on load", on_load), ("fused tail", tail), ("relay", relay)):
+            assert_close(got, plain.cpu(), name)
+        # autograd on: same keywords, gradients flow through the unfused ops
+        xg = x.clone().requires_grad_(True)
+        y = c2(c1(xg, relu_so3_fft=c2.b_out), input_spectrum=True, relu_integrate=True)
+        assert_close(y, plain.cpu(), "relay keywords with autograd")
+        y.sum().backward()
+        assert xg.grad is not None and torch.isfinite(xg.grad).all()
+        assert c1.kernel.grad is not None and c2.kernel.grad is not None
