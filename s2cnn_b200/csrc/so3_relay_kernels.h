@@ -153,6 +153,43 @@ struct so3_relay_fused_impl {
       const int grp = bg0 / p.BG;
       const bool landed = bulk_wait(ctx, wbar, (unsigned)(grp & 1));
       const float* wslice = landed ? Wg : p.win_g + (size_t)grp * p.win_stride;
+      if (p.BG == 4 && ZG == 4) {
+        // groups of four betas: one frequency pair per work item with all 4 x 4 (beta, batch
+        // element) accumulators in registers - three 16-byte loads feed 32 multiply-adds
+        for (int pr = ctx.tid; pr < p.pin.npairs; pr += ctx.nthr) {
+          const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
+          const float4* w4 = reinterpret_cast<const float4*>(wslice + info.x * 4);
+          const float4* x4 = reinterpret_cast<const float4*>(Xh + info.x * ZG);
+          float2 s[4][ZG];
+#pragma unroll
+          for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) s[bi][z] = make_float2(0.f, 0.f);
+          for (int li = 0; li < info.y; ++li) {
+            const float4 w = w4[li], xa = x4[2 * li], xb = x4[2 * li + 1];
+            const float wv[4] = {w.x, w.y, w.z, w.w};
+            const float2 xv[ZG] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w),
+                                   make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
+#pragma unroll
+            for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+              for (int z = 0; z < ZG; ++z) {
+                s[bi][z].x = fmaf(wv[bi], xv[z].x, s[bi][z].x);
+                s[bi][z].y = fmaf(wv[bi], xv[z].y, s[bi][z].y);
+              }
+          }
+          float2* pl = planes + info.z * KP + info.w;
+          const bool mirror = (info.w == 0 && info.z > 0);  // n = 0, m > 0: row N - m holds the conjugate
+#pragma unroll
+          for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) {
+              float2* dst = pl + (size_t)(z * 4 + bi) * plane_sz;
+              dst[0] = s[bi][z];
+              if (mirror) dst[(N - 2 * info.z) * KP] = make_float2(s[bi][z].x, -s[bi][z].y);
+            }
+        }
+      } else
       for (int it = ctx.tid; it < p.pin.npairs * bc; it += ctx.nthr) {
         const int pr = it / bc, bi = it - pr * bc;
         const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
