@@ -115,6 +115,13 @@ int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_
  * and the head of the next SO3Convolution.forward (s2cnn/soft/so3_conv.py:50). */
 int s2c_s2_conv_relu_so3_rfft(const float* xs, const float* ys, float* out, int nbatch, int f_in,
                               int f_out, int b, int b_next, const float* bias, void* stream);
+/* The same relay between two SO3Convolutions:
+ *   out = so3_rfft(relu(so3_rifft(x, b_out = b_mid) + bias), b_out = b_next)
+ * x [nspec(b_in), nbatch, 2], out [nspec(b_next), nbatch, 2]; bias [nfeature] or NULL as in
+ * s2c_so3_rifft.  Only for 2 b_mid <= 32, b_in <= b_mid, b_next <= b_mid.  Replaces the tail of one
+ * SO3Convolution.forward (s2cnn/soft/so3_conv.py:55-56), the ReLU and the head of the next (:50). */
+int s2c_so3_rifft_relu_rfft(const float* x, float* out, long nbatch, int b_in, int b_mid, int b_next,
+                            const float* bias, int nfeature, void* stream);
 /* Same result as s2c_so3_rifft, for callers that cannot obtain device memory at call time (a
  * process whose GPU memory is wholly pre-reserved by another allocator, or a loop that must avoid
  * the device-wide synchronisation of cudaMalloc/cudaFree): no workspace argument and no device

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "s2c_so3_rifft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P, c_size_t, _P]),
     "s2c_so3_rifft_relu_integrate": (c_int, [_P, _P, c_long, c_int, c_int, _P, c_int, _P]),
     "s2c_s2_conv_relu_so3_rfft": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P]),
+    "s2c_so3_rifft_relu_rfft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P]),
     "s2c_so3_rifft_static": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P]),
     "s2c_so3_rifft_static_max_bytes": (c_size_t, []),
     "s2c_s2_conv_synthesis_workspace": (c_size_t, [c_int, c_int, c_int]),

@@ -530,34 +530,57 @@ static int relay_bg(int N, int Kin, int nrows_in, int nrows_out) {
   return best3 ? best3 : best;
 }
 
+// relay kernel: synthesis at bandwidth b_mid of a spectrum of bandwidth b_in (plain, or the s2_mm
+// product of xs and ys when xs is set), + bias, ReLU, analysis to bandwidth b_next
+static int relay_launch(const float2* x, const float2* xs, const float2* ys, int s2_nb, int s2_fin,
+                        float* out, long nz, int nfeat, int b_in, int b_mid, int b_next,
+                        const float* bias, stream_t st, const char* who) {
+  const int N = 2 * b_mid;
+  if (N > kFusedMaxN || b_next > b_mid || b_in > b_mid)
+    return fail(S2C_ERR_UNSUPPORTED,
+                std::string(who) + ": needs 2 b <= 32, b_in <= b and b_next <= b");
+  FftDev fft;
+  RelayParams f;
+  S2C_TRY(TableCache::get().fft(N, fft));
+  S2C_TRY(TableCache::get().panels(b_mid, b_in, b_in, false, false, f.pin));
+  S2C_TRY(TableCache::get().panels(b_mid, b_next, b_next, true, false, f.pout));
+  f.BG = relay_bg(N, b_in, f.pin.nrows, f.pout.nrows);
+  if (f.BG < 1) return fail(S2C_ERR_UNSUPPORTED, std::string(who) + ": shared memory");
+  S2C_TRY(TableCache::get().grouped(b_mid, b_in, b_in, false, f.BG, &f.win_g, &f.win_stride));
+  f.x = x; f.x_zstride = nz;
+  f.xs = xs; f.ys = ys;
+  f.s2_nb = s2_nb; f.s2_fin = s2_fin; f.s2_fout = nfeat;
+  f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1;
+  f.out = (float2*)out; f.out_zstride = nz;
+  f.tw = fft.tw;
+  f.nbatch = (int)nz; f.Kin = b_in; f.Kout = b_next;
+  f.KP = fused_kp(N); f.PS = fused_plane_stride(N, b_in);
+  int rc = S2C_OK;
+  const long grid = (nz + kFusedZG - 1) / kFusedZG;
+  const size_t sm = relay_smem_bytes(N, b_in, f.pin.nrows, f.pout.nrows, f.BG);
+  S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_relay_fused, kN, grid, 256, sm, st, f));
+  return rc;
+}
+
 int s2c_s2_conv_relu_so3_rfft(const float* xs, const float* ys, float* out, int nbatch, int f_in,
                               int f_out, int b, int b_next, const float* bias, void* stream) {
   S2C_TRY(check_b(b, b_next));
   if (!xs || !ys || !out || nbatch < 1 || f_in < 1 || f_out < 1)
     return fail(S2C_ERR_BAD_ARG, "s2c_s2_conv_relu_so3_rfft: bad argument");
-  const int N = 2 * b;
-  if (N > kFusedMaxN || b_next > b)
-    return fail(S2C_ERR_UNSUPPORTED, "s2c_s2_conv_relu_so3_rfft: needs 2 b <= 32 and b_next <= b");
-  FftDev fft;
-  RelayParams f;
-  S2C_TRY(TableCache::get().fft(N, fft));
-  S2C_TRY(TableCache::get().panels(b, b, b, false, false, f.pin));
-  S2C_TRY(TableCache::get().panels(b, b_next, b_next, true, false, f.pout));
-  f.BG = relay_bg(N, b, f.pin.nrows, f.pout.nrows);
-  if (f.BG < 1) return fail(S2C_ERR_UNSUPPORTED, "s2c_s2_conv_relu_so3_rfft: shared memory");
-  S2C_TRY(TableCache::get().grouped(b, b, b, false, f.BG, &f.win_g, &f.win_stride));
-  f.xs = (const float2*)xs; f.ys = (const float2*)ys;
-  f.s2_nb = nbatch; f.s2_fin = f_in; f.s2_fout = f_out;
-  f.bias = bias; f.nfeat = f_out;
-  f.out = (float2*)out; f.out_zstride = (long)nbatch * f_out;
-  f.tw = fft.tw;
-  f.nbatch = nbatch * f_out; f.Kin = b; f.Kout = b_next;
-  f.KP = fused_kp(N); f.PS = fused_plane_stride(N, b);
-  int rc = S2C_OK;
-  const long grid = ((long)f.nbatch + kFusedZG - 1) / kFusedZG;
-  const size_t sm = relay_smem_bytes(N, b, f.pin.nrows, f.pout.nrows, f.BG);
-  S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_relay_fused, kN, grid, 256, sm, as_stream(stream), f));
-  return rc;
+  return relay_launch(nullptr, (const float2*)xs, (const float2*)ys, nbatch, f_in, out,
+                      (long)nbatch * f_out, f_out, b, b, b_next, bias, as_stream(stream),
+                      "s2c_s2_conv_relu_so3_rfft");
+}
+
+int s2c_so3_rifft_relu_rfft(const float* x, float* out, long nbatch, int b_in, int b_mid, int b_next,
+                            const float* bias, int nfeature, void* stream) {
+  S2C_TRY(check_b(b_in, b_mid));
+  S2C_TRY(check_b(b_mid, b_next));
+  if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_relu_rfft: bad argument");
+  if (bias && nfeature < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_relu_rfft: nfeature must be >= 1 with a bias");
+  return relay_launch((const float2*)x, nullptr, nullptr, 0, 0, out, nbatch, bias ? nfeature : 0,
+                      b_in, b_mid, b_next, bias, as_stream(stream), "s2c_so3_rifft_relu_rfft");
 }
 
 size_t s2c_s2_conv_synthesis_workspace(int nbatch, int f_out, int b) {

@@ -1,6 +1,7 @@
 // Two layers' worth of transforms in one kernel, for small bandwidths (N = 2b <= 32):
 //
 //   S2Convolution tail      z = so3_rifft(s2_mm(xs, ys)) + bias        (s2cnn/soft/s2_conv.py:42-45)
+//     or SO3Convolution tail  z = so3_rifft(x) + bias                  (s2cnn/soft/so3_conv.py:55-56)
 //   activation              relu(z)
 //   SO3Convolution head     so3_rfft(relu(z), b_out = b_next)          (s2cnn/soft/so3_conv.py:50)
 //
@@ -20,7 +21,10 @@
 namespace s2c {
 
 struct RelayParams {
-  // synthesis side: spectrum = s2_mm(xs, ys) computed on the fly
+  // synthesis side: either a plain SO(3) spectrum x (rows of x_zstride complex) ...
+  const float2* x;
+  long x_zstride;
+  // ... or, when xs is set, spectrum = s2_mm(xs, ys) computed on the fly
   const float2* xs;    // [Kin^2, s2_nb, s2_fin]
   const float2* ys;    // [Kin^2, s2_fin, s2_fout]
   int s2_nb, s2_fin, s2_fout;
@@ -80,7 +84,35 @@ struct so3_relay_fused_impl {
     // X[l,m,n](i,j) = sum_k xs[l,m,i,k] conj(ys[l,n,k,j]).  The block's batch elements are
     // (i, j .. j+3) when f_out is a multiple of 4: one work item per panel row then serves all four
     // (xs loaded once, ys with 16-byte loads); otherwise one item per (row, batch element).
-    if (zc == ZG && ZG == 4 && p.s2_fout % ZG == 0) {
+    if (!p.xs) {
+      // plain spectrum: the block's batch elements are 32 contiguous bytes of every row
+      const bool vec = zc == ZG && ZG == 4 && p.x_zstride % 2 == 0;
+      for (int r = ctx.tid; r < nrows_in; r += ctx.nthr) {
+        int l, m, n;
+        rowmap_unpack(p.pin.rowmap[r], l, m, n);
+        const float2* pa = p.x + so3_row(l, m, n) * p.x_zstride + z0;
+        const float2* pb = p.x + so3_row(l, -m, -n) * p.x_zstride + z0;
+        float2 av[ZG], bv[ZG];
+        if (vec) {
+          const float4 a01 = reinterpret_cast<const float4*>(pa)[0], a23 = reinterpret_cast<const float4*>(pa)[1];
+          const float4 b01 = reinterpret_cast<const float4*>(pb)[0], b23 = reinterpret_cast<const float4*>(pb)[1];
+          av[0] = make_float2(a01.x, a01.y); av[1] = make_float2(a01.z, a01.w);
+          av[2] = make_float2(a23.x, a23.y); av[3] = make_float2(a23.z, a23.w);
+          bv[0] = make_float2(b01.x, b01.y); bv[1] = make_float2(b01.z, b01.w);
+          bv[2] = make_float2(b23.x, b23.y); bv[3] = make_float2(b23.z, b23.w);
+        } else {
+#pragma unroll
+          for (int z = 0; z < ZG; ++z) {
+            av[z] = z < zc ? pa[z] : make_float2(0.f, 0.f);
+            bv[z] = z < zc ? pb[z] : make_float2(0.f, 0.f);
+          }
+        }
+        const float fudge = ((m - n) & 1) ? -1.f : 1.f;
+#pragma unroll
+        for (int z = 0; z < ZG; ++z)
+          Xh[r * ZG + z] = make_float2(0.5f * (av[z].x + fudge * bv[z].x), 0.5f * (av[z].y - fudge * bv[z].y));
+      }
+    } else if (zc == ZG && ZG == 4 && p.s2_fout % ZG == 0) {
       const int pi = (int)(z0 / p.s2_fout), pj = (int)(z0 - (long)pi * p.s2_fout);
       for (int r = ctx.tid; r < nrows_in; r += ctx.nthr) {
         int l, m, n;

@@ -164,6 +164,28 @@ class Ops:
                           nbatch, f_in, f_out, b, b_next, bias_ptr, self._stream(xs))
         return out
 
+    def so3_rifft_relu_rfft(self, x, bias, b_mid, b_next):
+        """so3_rfft(relu(so3_rifft(x, b_out=b_mid) + bias), b_out=b_next) in one kernel (2 b_mid <= 32).
+        x [nspec(b_in), ..., 2] -> [nspec(b_next), ..., 2]"""
+        self._prep(x, bias)
+        assert x.size(-1) == 2
+        b_in = bandwidth_from_so3_nspec(x.size(0))
+        lead = tuple(x.shape[1:-1])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        nfeat = 0
+        bias_ptr = None
+        if bias is not None:
+            bias = bias.contiguous().view(-1)
+            nfeat = bias.numel()
+            assert len(lead) >= 1 and lead[-1] == nfeat, (lead, nfeat)
+            bias_ptr = bias.data_ptr()
+        out = x.new_empty((so3_nspec(b_next),) + lead + (2,))
+        with self._ctx(x):
+            self.lib.call("s2c_so3_rifft_relu_rfft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_mid,
+                          b_next, bias_ptr, nfeat, self._stream(x))
+        return out
+
     def s2_conv_synthesis(self, xs, ys, bias=None):
         """so3_rifft(s2_mm(xs, ys)) + bias without materialising the SO(3) spectrum (small b).
         xs [b^2, batch, f_in, 2], ys [b^2, f_in, f_out, 2] -> [batch, f_out, 2b, 2b, 2b]"""

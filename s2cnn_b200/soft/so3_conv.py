@@ -33,11 +33,14 @@ class SO3Convolution(Module):
         # the scaling stays outside the parameter (so3_conv.py:30-34)
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
 
-    def forward(self, x, relu_input=False, relu_integrate=False, input_spectrum=False):  # pylint: disable=W
+    def forward(self, x, relu_input=False, relu_integrate=False, input_spectrum=False,
+                relu_so3_fft=None):  # pylint: disable=W
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
         :input_spectrum: (extension) x is already SO3_fft_real(signal, b_out), as returned by
                          ``S2Convolution.forward(..., relu_so3_fft=b_out)``
+        :relu_so3_fft: (extension) bandwidth b_next of the SO3Convolution that follows: return that
+                       layer's input spectrum SO3_fft_real(relu(conv(x)), b_next) (see S2Convolution)
         :relu_input: (extension) compute conv(relu(x)); the activation is applied while x is read
         :relu_integrate: (extension) return so3_integrate(relu(conv(x))) [batch, feature_out]; without
                          autograd and for 2 b_out <= 32 the output signal is never written
@@ -60,6 +63,12 @@ class SO3Convolution(Module):
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)
         z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
+        if relu_so3_fft is not None:
+            b_next = int(relu_so3_fft)
+            if (2 * self.b_out <= 32 and b_next <= self.b_out and
+                    not (torch.is_grad_enabled() and (z.requires_grad or self.bias.requires_grad))):
+                return cuda_ops().so3_rifft_relu_rfft(z, self.bias, self.b_out, b_next)
+            return SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(z, self.bias)), b_next)
         if relu_integrate:
             if 2 * self.b_out <= 32 and not (torch.is_grad_enabled() and (z.requires_grad or self.bias.requires_grad)):
                 return cuda_ops().so3_rifft_relu_integrate(z, bias=self.bias)  # [batch, feature_out]

@@ -347,6 +347,22 @@ def test_two_layer_relay_kernel(backend, b, b_next, nb, fi, fo):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_mid,b_next,lead", [(6, 6, 4, (3, 4)), (4, 7, 5, (2, 3)), (10, 10, 5, (5,)),
+                                                     (5, 5, 5, (2, 2))])
+def test_relay_kernel_between_so3_layers(backend, b_in, b_mid, b_next, lead):
+    """so3_rfft(relu(so3_rifft(x, b_mid) + bias), b_next) in one kernel for a plain spectrum."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(b_in * 17 + b_next)
+    x = torch.randn(n3(b_in), *lead, 2, generator=gen)
+    bias = torch.randn(lead[-1], generator=gen)
+    shape = (1,) * (len(lead) - 1) + (lead[-1], 1, 1, 1)
+    ref = O.so3_rfft(torch.relu(O.so3_rifft(x, b_out=b_mid) + bias.view(shape)), b_out=b_next)
+    assert_close(ops.so3_rifft_relu_rfft(x.to(dev), bias.to(dev), b_mid, b_next), ref, "relay")
+    ref0 = O.so3_rfft(torch.relu(O.so3_rifft(x, b_out=b_mid)), b_out=b_next)
+    assert_close(ops.so3_rifft_relu_rfft(x.to(dev), None, b_mid, b_next), ref0, "relay, no bias")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b,nb,fi,fo", [(4, 3, 2, 3), (6, 5, 1, 4), (1, 2, 3, 2), (10, 2, 1, 6)])
 def test_s2_product_synthesis_fused(backend, b, nb, fi, fo):
     """so3_rifft(s2_mm(x, y)) + bias in one call, single-kernel path and general path."""
