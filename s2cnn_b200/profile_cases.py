@@ -7,6 +7,8 @@ within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hun
 
     inv10   so3_rifft, b = 10, 5120 signals          (kernel so3_inv_fused<20>)
     fwd10   so3_rfft,  b = 10 -> 6, 5120 signals     (kernel so3_fwd_fused<20>)
+    relay10 s2_mm + so3_rifft (b = 10) + bias + ReLU + so3_rfft (-> b = 6), batch 256, 1 -> 20
+            features = 5120 signals                  (kernel so3_relay_fused<20>)
     mm      so3_mm, nl = 6, batch 256, 20 -> 40      (kernel so3_mm_tc_kernel)
     mm_c4   so3_mm, nl = 10, batch 32, 100 -> 100    (kernel so3_mm_tc_kernel at a GEMM-sized case)
     fft64   so3_rfft + so3_rifft, b = 64, 8 signals  (plane kernels + Wigner contraction)
@@ -31,6 +33,12 @@ def main(which):
         x = torch.randn(5120, 20, 20, 20, device=dev)
         for _ in range(3):
             ops.so3_rfft(x, b_out=6)
+    elif which == "relay10":
+        xs = torch.randn(100, 256, 1, 2, device=dev)
+        ys = torch.randn(100, 1, 20, 2, device=dev)
+        bias = torch.randn(20, device=dev)
+        for _ in range(3):
+            ops.s2_conv_relu_so3_rfft(xs, ys, bias, 6)
     elif which == "mm":
         x = torch.randn(so3_nspec(6), 256, 20, 2, device=dev)
         y = torch.randn(so3_nspec(6), 20, 40, 2, device=dev)
