@@ -57,7 +57,11 @@ struct so3_relay_fused_impl {
     const int Kin = p.Kin, Kout = p.Kout, KP = p.KP;
     const int nrows_in = p.pin.nrows, nrows_out = p.pout.nrows;
     float2* tw = reinterpret_cast<float2*>(smem);
-    float2* Xh = tw + N;                                                    // [nrows_in][ZG]
+    // half spectrum, split in two arrays of 16-byte rows: [nrows_in][z 0,1] then [nrows_in][z 2,3]
+    // (rows of consecutive frequency pairs then start 16 L instead of 32 L bytes apart, which
+    // halves the bank conflicts of the per-pair 16-byte loads)
+    float2* Xh = tw + N;
+    auto xh_at = [&](int r, int z) -> float2& { return Xh[((z >> 1) * nrows_in + r) * 2 + (z & 1)]; };
     int4* pinfo = reinterpret_cast<int4*>(Xh + (size_t)nrows_in * ZG);      // [npairs_in]
     float* Wg = reinterpret_cast<float*>(pinfo + p.pin.npairs);             // [nrows_in][BG]
     unsigned long long* wbar = reinterpret_cast<unsigned long long*>(Wg + p.win_stride);
@@ -110,7 +114,7 @@ struct so3_relay_fused_impl {
         const float fudge = ((m - n) & 1) ? -1.f : 1.f;
 #pragma unroll
         for (int z = 0; z < ZG; ++z)
-          Xh[r * ZG + z] = make_float2(0.5f * (av[z].x + fudge * bv[z].x), 0.5f * (av[z].y - fudge * bv[z].y));
+          xh_at(r, z) = make_float2(0.5f * (av[z].x + fudge * bv[z].x), 0.5f * (av[z].y - fudge * bv[z].y));
       }
     } else if (zc == ZG && ZG == 4 && p.s2_fout % ZG == 0) {
       const int pi = (int)(z0 / p.s2_fout), pj = (int)(z0 - (long)pi * p.s2_fout);
@@ -149,7 +153,7 @@ struct so3_relay_fused_impl {
         const float fudge = ((m - n) & 1) ? -1.f : 1.f;
 #pragma unroll
         for (int z = 0; z < ZG; ++z)
-          Xh[r * ZG + z] = make_float2(0.5f * (av[z].x + fudge * bv[z].x), 0.5f * (av[z].y - fudge * bv[z].y));
+          xh_at(r, z) = make_float2(0.5f * (av[z].x + fudge * bv[z].x), 0.5f * (av[z].y - fudge * bv[z].y));
       }
     } else {
     for (int it = ctx.tid; it < nrows_in * ZG; it += ctx.nthr) {
@@ -174,7 +178,7 @@ struct so3_relay_fused_impl {
         }
       }
       const float fudge = ((m - n) & 1) ? -1.f : 1.f;
-      Xh[it] = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
+      xh_at(r, zz) = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
     }
     }
     ctx.sync();
@@ -191,14 +195,15 @@ struct so3_relay_fused_impl {
         for (int pr = ctx.tid; pr < p.pin.npairs; pr += ctx.nthr) {
           const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
           const float4* w4 = reinterpret_cast<const float4*>(wslice + info.x * 4);
-          const float4* x4 = reinterpret_cast<const float4*>(Xh + info.x * ZG);
+          const float4* xa4 = reinterpret_cast<const float4*>(Xh) + info.x;
+          const float4* xb4 = xa4 + nrows_in;
           float2 s[4][ZG];
 #pragma unroll
           for (int bi = 0; bi < 4; ++bi)
 #pragma unroll
             for (int z = 0; z < ZG; ++z) s[bi][z] = make_float2(0.f, 0.f);
           for (int li = 0; li < info.y; ++li) {
-            const float4 w = w4[li], xa = x4[2 * li], xb = x4[2 * li + 1];
+            const float4 w = w4[li], xa = xa4[li], xb = xb4[li];
             const float wv[4] = {w.x, w.y, w.z, w.w};
             const float2 xv[ZG] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w),
                                    make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
@@ -226,7 +231,7 @@ struct so3_relay_fused_impl {
         const int pr = it / bc, bi = it - pr * bc;
         const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
         const float* w = wslice + info.x * p.BG + bi;
-        const float2* xr = Xh + info.x * ZG;
+        const int xrow = info.x;
         float2 s[ZG];
 #pragma unroll
         for (int z = 0; z < ZG; ++z) s[z] = make_float2(0.f, 0.f);
@@ -234,7 +239,7 @@ struct so3_relay_fused_impl {
           const float wv = w[li * p.BG];
 #pragma unroll
           for (int z = 0; z < ZG; ++z) {
-            const float2 xv = xr[li * ZG + z];
+            const float2 xv = xh_at(xrow + li, z);
             s[z].x = fmaf(wv, xv.x, s[z].x);
             s[z].y = fmaf(wv, xv.y, s[z].y);
           }
