@@ -80,14 +80,6 @@ int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, i
  * "unsupported". */
 int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_out,
                       void* workspace, size_t workspace_bytes, void* stream);
-/* Test switches (no counterpart in the reference).  level 1 routes small bandwidths (2b <= 32)
- * through the general kernels instead of the single-kernel path; level 2 additionally replaces the
- * plane kernels of 2b = 64 / 128 (both row transforms of a (z, beta) plane in one kernel) by the
- * three separate passes every other size uses; 0 restores the defaults. */
-void s2c_debug_force_general_path(int level);
-/* Plane kernels: 0 (default) = thread-block clusters of 4 beta planes exchanging through
- * distributed shared memory; 1 = independent blocks, no clusters. */
-void s2c_debug_plane_width(int planes);
 /* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].
  * Replaces so3_fft, s2cnn/soft/so3_fft.py:12-61. */
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
@@ -126,9 +118,11 @@ int s2c_so3_rifft_relu_rfft(const float* x, float* out, long nbatch, int b_in, i
  * process whose GPU memory is wholly pre-reserved by another allocator, or a loop that must avoid
  * the device-wide synchronisation of cudaMalloc/cudaFree): no workspace argument and no device
  * allocation inside.  Scratch and tables live in two static device arrays that every GPU loading
- * the library holds until exit (32 MiB + 4 MiB).  A call whose scratch need
- * (s2c_so3_fft_workspace_min(b_in, b_out) * nbatch) exceeds s2c_so3_rifft_static_max_bytes(), or
- * whose tables exceed 4 MiB, is rejected with an error.  The first call on a device, and any call
+ * the library holds until exit (32 MiB + 4 MiB).  A call whose scratch need - nbatch *
+ * (K N^2 + K (2K - 1) N) * 8 bytes with N = 2 b_out and K = min(b_in, b_out), which equals
+ * s2c_so3_fft_workspace_min(b_in, b_out) * nbatch when b_in <= b_out and is smaller otherwise -
+ * exceeds s2c_so3_rifft_static_max_bytes(), or whose tables exceed 4 MiB, is rejected with an
+ * error.  The first call on a device, and any call
  * that changes (b_in, b_out, for_grad), looks up the arrays' device addresses and uploads tables
  * synchronously: issue it before any stream capture.  All calls on a device share the arrays, so
  * calls that overlap on the GPU (other streams or threads) race; nothing has to be cleared between
@@ -221,6 +215,19 @@ int s2c_so3_rotation_matrices(int b, double alpha, double beta, double gamma, fl
  * s2cnn/soft/so3_rotation.py:22-41 (and, with adjoint, its autograd). */
 int s2c_so3_rotate_spectrum(const float* U, const float* x, float* z, int b, long nbatch,
                             int adjoint, void* stream);
+
+/* ---- test hooks (not part of the drop-in surface; no counterpart in the reference) ------------ */
+/* Path selection for the test-suite, so that every kernel variant can be compared with the oracle
+ * at the same sizes.  The switches are process-wide atomics read once per call by the dispatcher;
+ * an application has no reason to touch them.
+ *   s2c_debug_force_general_path(level): 1 routes small bandwidths (2b <= 32) through the general
+ *     kernels instead of the single-kernel path; 2 additionally replaces the plane kernels of
+ *     2b = 64 / 128 (both row transforms of a (z, beta) plane in one kernel) by the three separate
+ *     passes every other size uses; 0 restores the defaults.
+ *   s2c_debug_plane_width(planes): plane kernels, 0 (default) = the fast variant, 1 = the simple
+ *     variant that touches the scratch array directly. */
+void s2c_debug_force_general_path(int level);
+void s2c_debug_plane_width(int planes);
 
 #ifdef __cplusplus
 }

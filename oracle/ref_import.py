@@ -1,9 +1,10 @@
 """Test infrastructure (oracle side): import the UNMODIFIED reference CPU code path.
 
 Only usable where a checkout of jonkhler/s2cnn is present (pass its path or set
-``S2CNN_REFERENCE``); it is used to validate ``oracle/s2cnn_oracle.py`` and to generate the
-golden fixtures under ``tests/golden/``.  Nothing at run time (GPU tests, smoke, bench) calls
-this module.
+``S2CNN_REFERENCE``) or where ``oracle/make_ref.py`` has left its untracked copy; it is used to
+validate ``oracle/s2cnn_oracle.py``, to generate the golden fixtures under ``tests/golden/`` and by
+the benchmark's CPU-baseline / reference arm to time the reference's own CPU code.  Neither the
+product nor the GPU tests call this module.
 
 The reference is seven years old; three shims are needed on a current stack, none of which
 touches its arithmetic:
@@ -33,7 +34,14 @@ import torch
 from . import wigner_np
 
 _DEFAULT_REF = os.environ.get("S2CNN_REFERENCE", "/root/reference")
+_LOCAL_COPY = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
 _state = {}
+
+
+def local_copy():
+    """Path of the untracked copy of the reference package made by ``oracle/make_ref.py`` (the form
+    in which the reference travels to a machine without a checkout), or None."""
+    return _LOCAL_COPY if os.path.isdir(os.path.join(_LOCAL_COPY, "s2cnn")) else None
 
 
 def _install_lie_learn_standin():

@@ -1,6 +1,6 @@
 """Small, fixed workloads for profiler captures of single kernels.
 
-    python -m s2cnn_b200.profile_cases <case>
+    python -m s2cnn_b200._profile_cases <case>
 
 Each case runs one op a few times on seeded synthetic data sized for a capture that ends by itself
 within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hundred MB at most):

@@ -14,12 +14,14 @@
 // and launched with S2C_LAUNCH(my_kernel, grid, block, smem_bytes, stream, params).
 #pragma once
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <cmath>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -131,11 +133,15 @@ struct TimingRec {
   const char* name;
   cudaEvent_t a, b;
 };
-inline bool& timing_on() {
-  static bool on = false;
+inline std::atomic<bool>& timing_on() {
+  static std::atomic<bool> on{false};
   return on;
 }
-inline std::vector<TimingRec>& timing_recs() {
+inline std::mutex& timing_mutex() {
+  static std::mutex m;
+  return m;
+}
+inline std::vector<TimingRec>& timing_recs() {   // guarded by timing_mutex()
   static std::vector<TimingRec> r;
   return r;
 }
@@ -160,6 +166,7 @@ inline int launch_impl(K kernel, const char* kname, long grid, int block, size_t
   kernel<<<(unsigned)grid, block, smem, stream>>>(p);
   if (timed) {
     cudaEventRecord(rec.b, stream);
+    std::lock_guard<std::mutex> lock(timing_mutex());
     timing_recs().push_back(rec);
   }
   ++g_launch_count;

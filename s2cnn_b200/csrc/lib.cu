@@ -4,6 +4,7 @@
 #include "../../include/s2cnn_b200.h"
 
 #include <algorithm>
+#include <atomic>
 #include <complex>
 
 #include "backend.h"
@@ -23,8 +24,9 @@
 
 namespace s2c {
 thread_local long g_launch_count = 0;
-static int g_force_general = 0;   // test switch: 1 = no single-kernel path, 2 = also no plane kernels
-static int g_plane_width = 0;     // plane kernels: 0 = clusters of planes exchanging V, 1 = no clusters
+// test switches (process-wide, race-free; see the "test hooks" section of the header)
+static std::atomic<int> g_force_general{0};   // 1 = no single-kernel path, 2 = also no plane kernels
+static std::atomic<int> g_plane_width{0};     // plane kernels: 0 = fast variant, 1 = simple variant
 
 #define S2C_TRY(expr)            \
   do {                           \
@@ -318,7 +320,10 @@ int s2c_is_cuda_build(void) {
 
 void s2c_timing_begin(void) {
 #ifndef S2C_EMUL
-  timing_recs().clear();
+  {
+    std::lock_guard<std::mutex> lock(timing_mutex());
+    timing_recs().clear();
+  }
   timing_on() = true;
 #endif
 }
@@ -328,6 +333,7 @@ int s2c_timing_end(char* buf, size_t buf_bytes) {
   buf[0] = 0;
 #ifndef S2C_EMUL
   timing_on() = false;
+  std::lock_guard<std::mutex> lock(timing_mutex());
   struct Acc { long n = 0; double ms = 0; };
   std::vector<std::pair<std::string, Acc>> acc;
   for (auto& r : timing_recs()) {
@@ -780,6 +786,9 @@ int s2c_so3_mm(const float* x, const float* y, float* z, int nl, int nb, int fi,
 
 int s2c_so3_mm_tc_status(void) {
 #ifndef S2C_EMUL
+  // wait for every stream of the device (the products run on the caller's streams, which a plain
+  // copy from the symbol would not be ordered after), then read the flag
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, g_tc_err_flag, sizeof(int)) != cudaSuccess) return -1;
   return v;
@@ -1008,10 +1017,15 @@ static int static_load_tables(StaticDeviceState& st, int b_beta, int K, bool wei
                 "s2c_so3_rifft_static: tables for these bandwidths need " + std::to_string(total) +
                     " bytes, the static table array holds " + std::to_string(kStaticTableBytes));
 #ifndef S2C_EMUL
-  // kernels of an earlier call on this stream may still be reading the old tables
+  // Kernels of an earlier call on this stream may still be reading the old tables.  Only the
+  // caller's stream is waited for: calls on other streams must not overlap this one anyway (they
+  // would race on the shared arrays, as the header says).
   S2C_TRY(cuda_check(cudaStreamSynchronize(stream), "stream sync before table reload"));
 #endif
   (void)stream;
+  // From here on the array no longer holds a complete table set: forget the old key first, so that
+  // a failed upload cannot leave a later call with the old bandwidths reading a half-written array.
+  st.b_beta = st.K = st.weighted = -1;
   S2C_TRY(dev_upload(st.tables + o_tw, tw.data(), tw.size() * sizeof(float)));
   S2C_TRY(dev_upload(st.tables + o_pos, pos.data(), pos.size() * sizeof(unsigned short)));
   S2C_TRY(dev_upload(st.tables + o_off, poff.data(), poff.size() * sizeof(long long)));
@@ -1050,6 +1064,7 @@ int s2c_so3_rifft_static(const float* x, float* out, long nbatch, int b_in, int 
   if (bias && nfeature < 1)
     return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_static: nfeature must be >= 1 with a bias");
   const int N = 2 * b_out, K = std::min(b_in, b_out);
+  // scratch of the synthesis: both arrays are laid out on the OUTPUT grid (2 b_out samples per axis)
   const size_t need = so3_ws_per_z(N, K) * (size_t)nbatch;
   if (need > kStaticScratchBytes)
     return fail(S2C_ERR_WORKSPACE,

@@ -9,6 +9,7 @@ from ..ops import cuda_ops
 from ..s2_ft import s2_rft
 from .s2_fft import S2_fft_real
 from .so3_fft import so3_rfft, SO3_fft_real
+from ._spectrum_cache import KernelSpectrumCache
 
 
 class _S2ProductSynthesis(torch.autograd.Function):
@@ -42,13 +43,15 @@ class _S2ProductSynthesis(torch.autograd.Function):
 
 class S2Convolution(Module):
     def __init__(self, nfeature_in, nfeature_out, b_in, b_out, grid):
-        '''
-        :param nfeature_in: number of input fearures
-        :param nfeature_out: number of output features
-        :param b_in: input bandwidth (precision of the input SOFT grid)
-        :param b_out: output bandwidth
-        :param grid: points of the sphere defining the kernel, tuple of (beta, alpha)'s
-        '''
+        """Correlation of a signal on the sphere with a learned kernel supported on a few points of
+        the sphere; the result is a signal on SO(3).
+
+        nfeature_in, nfeature_out: channel counts of the input and output signals.
+        b_in, b_out: bandwidths; the input lives on the 2 b_in x 2 b_in sphere grid, the output on
+            the (2 b_out)^3 SOFT grid.
+        grid: the points (beta, alpha) on which the kernel has a weight, a tuple of 2-tuples;
+            ``kernel`` holds one weight per (input channel, output channel, point).
+        """
         super().__init__()
         self.nfeature_in = nfeature_in
         self.nfeature_out = nfeature_out
@@ -59,8 +62,9 @@ class S2Convolution(Module):
         self.kernel = Parameter(torch.empty(nfeature_in, nfeature_out, len(grid)).uniform_(-1, 1))
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 4.) / (self.b_in ** 2.))
         self.bias = Parameter(torch.zeros(1, nfeature_out, 1, 1, 1))
+        self._spectrum_cache = KernelSpectrumCache()
 
-    def forward(self, x, relu_so3_fft=None):  # pylint: disable=W
+    def forward(self, x, relu_so3_fft=None):
         '''
         :x:      [batch, feature_in,  beta, alpha]
         :relu_so3_fft: (extension) bandwidth b_next of the SO3Convolution that follows: return
@@ -75,7 +79,8 @@ class S2Convolution(Module):
         needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.kernel.requires_grad or
                                                   self.bias.requires_grad)
         x = S2_fft_real.apply(x, self.b_out)  # [l * m, batch, feature_in, complex]
-        y = s2_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m, feature_in, feature_out, complex]
+        # [l * m, feature_in, feature_out, complex]; kept between calls while the weights stand still
+        y = self._spectrum_cache.get(self.kernel, lambda k: s2_rft(k * self.scaling, self.b_out, self.grid))
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
             if not needs_grad and 2 * self.b_out <= 32 and b_next <= self.b_out:

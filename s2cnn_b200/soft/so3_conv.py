@@ -11,17 +11,19 @@ from ..so3_ft import so3_rft
 from ..so3_mm import so3_mm
 from .so3_fft import SO3_fft_real, SO3_fft_real_relu, SO3_ifft_real_bias
 from .so3_integrate import so3_relu_integrate
+from ._spectrum_cache import KernelSpectrumCache
 
 
 class SO3Convolution(Module):
     def __init__(self, nfeature_in, nfeature_out, b_in, b_out, grid):
-        '''
-        :param nfeature_in: number of input fearures
-        :param nfeature_out: number of output features
-        :param b_in: input bandwidth (precision of the input SOFT grid)
-        :param b_out: output bandwidth
-        :param grid: points of the SO(3) group defining the kernel, tuple of (beta, alpha, gamma)'s
-        '''
+        """Correlation of an SO(3) signal with a learned kernel supported on a few group elements.
+
+        nfeature_in, nfeature_out: channel counts of the input and output signals.
+        b_in, b_out: bandwidths; the input lives on the (2 b_in)^3 SOFT grid, the output on the
+            (2 b_out)^3 one.
+        grid: the rotations (beta, alpha, gamma) on which the kernel has a weight, a tuple of
+            3-tuples; ``kernel`` holds one weight per (input channel, output channel, rotation).
+        """
         super().__init__()
         self.nfeature_in = nfeature_in
         self.nfeature_out = nfeature_out
@@ -32,9 +34,10 @@ class SO3Convolution(Module):
         self.bias = Parameter(torch.zeros(1, nfeature_out, 1, 1, 1))
         # the scaling stays outside the parameter (so3_conv.py:30-34)
         self.scaling = 1. / math.sqrt(len(self.grid) * self.nfeature_in * (self.b_out ** 3.) / (self.b_in ** 3.))
+        self._spectrum_cache = KernelSpectrumCache()
 
     def forward(self, x, relu_input=False, relu_integrate=False, input_spectrum=False,
-                relu_so3_fft=None):  # pylint: disable=W
+                relu_so3_fft=None):
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
         :input_spectrum: (extension) x is already SO3_fft_real(signal, b_out), as returned by
@@ -59,7 +62,8 @@ class SO3Convolution(Module):
                 if relu_input:
                     x = torch.relu(x)
                 x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
-        y = so3_rft(self.kernel * self.scaling, self.b_out, self.grid)  # [l * m * n, feature_in, feature_out, complex]
+        # [l * m * n, feature_in, feature_out, complex]; kept between calls while the weights stand still
+        y = self._spectrum_cache.get(self.kernel, lambda k: so3_rft(k * self.scaling, self.b_out, self.grid))
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)
         z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
@@ -77,9 +81,10 @@ class SO3Convolution(Module):
 
 
 class SO3Shortcut(Module):
-    '''
-    Useful for ResNet
-    '''
+    """Skip connection for residual blocks: the identity when channel count and bandwidth are
+    unchanged, otherwise an SO3Convolution whose kernel sits on the identity rotation alone (a
+    per-channel mixing plus band limitation).  Parameters appear under ``conv.`` in the state dict
+    as in the reference (so3_conv.py:61-85)."""
 
     def __init__(self, nfeature_in, nfeature_out, b_in, b_out):
         super().__init__()
@@ -91,11 +96,8 @@ class SO3Shortcut(Module):
         else:
             self.conv = None
 
-    def forward(self, x):  # pylint: disable=W
-        '''
-        :x:      [batch, feature_in,  beta, alpha, gamma]
-        :return: [batch, feature_out, beta, alpha, gamma]
-        '''
+    def forward(self, x):
+        """[batch, feature_in, 2 b_in, 2 b_in, 2 b_in] -> [batch, feature_out, 2 b_out, 2 b_out, 2 b_out]"""
         if self.conv is not None:
             return self.conv(x)
         return x

@@ -6,6 +6,15 @@ weight and bias gradients against the oracle, within the stated tolerance (relat
   config 1   SO3Convolution 20 -> 40, b 10 -> 6, so3_near_identity_grid(pi/8, 2 pi, 8, 3, 8), fwd + bwd
   config 3   S2Conv -> ReLU -> SO3Conv -> ReLU -> so3_integrate -> Linear(40 -> 10), forward,
              with the activations fused the way bench.py runs the network
+  config 4   the three layers of the deep model at their real sizes (the shapes of the reference's
+             examples/shrec17/model.py:11-12), batch 2, each with input, kernel and bias gradients:
+             S2Convolution 6 -> 100, b 64 -> 16, s2_near_identity_grid(max_beta = pi/32)
+             SO3Convolution 100 -> 100, b 16 -> 10   (general-path analysis at 2b = 32, tensor-core
+                                                      products with K up to 3800)
+             SO3Convolution 100 -> 255, b 10 -> 5    (odd feature count: 8-byte tensor-core variant;
+                                                      few output tiles: the grad-y product is split
+                                                      over the outer index and summed atomically)
+             and the whole training step (cross-entropy, backward) against the oracle's autograd.
 """
 import numpy as np
 import pytest
@@ -88,3 +97,81 @@ def test_config3_network_forward_fused_activations():
     assert_close(fused, ref, "config 3 logits, ReLUs applied on load")
     assert_close(tail, ref, "config 3 logits, ReLU + integration inside the synthesis")
     assert_close(relay, ref, "config 3 logits, both layers' transforms in one kernel")
+
+
+def _c4_grids():
+    import s2cnn_b200 as S
+    g2 = S.s2_near_identity_grid(max_beta=np.pi / 32, n_alpha=8, n_beta=3)
+    g3 = S.so3_near_identity_grid(max_beta=np.pi / 8, max_gamma=2 * np.pi, n_alpha=8, n_beta=3,
+                                  n_gamma=8)
+    return g2, g3
+
+
+def test_config4_first_layer_s2_convolution_b64_to_16():
+    import s2cnn_b200 as S
+    g2, _ = _c4_grids()
+    torch.manual_seed(40)
+    conv = S.S2Convolution(6, 100, 64, 16, g2)
+    x = torch.randn(2, 6, 128, 128)
+    _check_layer(conv, O.s2_convolution, x, 64, 16, g2, "config 4 layer 1")
+
+
+def test_config4_second_layer_so3_convolution_b16_to_10():
+    import s2cnn_b200 as S
+    _, g3 = _c4_grids()
+    torch.manual_seed(41)
+    conv = S.SO3Convolution(100, 100, 16, 10, g3)
+    x = torch.randn(2, 100, 32, 32, 32)
+    _check_layer(conv, O.so3_convolution, x, 16, 10, g3, "config 4 layer 2")
+
+
+def test_config4_third_layer_so3_convolution_b10_to_5_split_grady():
+    import s2cnn_b200 as S
+    _, g3 = _c4_grids()
+    torch.manual_seed(42)
+    conv = S.SO3Convolution(100, 255, 10, 5, g3)
+    x = torch.randn(2, 100, 20, 20, 20)
+    _check_layer(conv, O.so3_convolution, x, 10, 5, g3, "config 4 layer 3")
+    from s2cnn_b200 import _lib
+    assert _lib.cuda_lib().s2c_so3_mm_tc_status() == 0
+
+
+def test_config4_training_step_matches_oracle_autograd():
+    """Forward, cross-entropy on random labels and backward of the whole deep model, batch 2:
+    logits, loss and every parameter gradient against the oracle's autograd."""
+    import s2cnn_b200 as S
+    g2, g3 = _c4_grids()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(44)
+    c1 = S.S2Convolution(6, 100, 64, 16, g2)
+    c2 = S.SO3Convolution(100, 100, 16, 10, g3)
+    c3 = S.SO3Convolution(100, 255, 10, 5, g3)
+    lin = torch.nn.Linear(255, 55)
+    x = torch.randn(2, 6, 128, 128)
+    labels = torch.randint(0, 55, (2,))
+
+    ref_params = [p.detach().clone().requires_grad_(True)
+                  for p in (c1.kernel, c1.bias, c2.kernel, c2.bias, c3.kernel, c3.bias,
+                            lin.weight, lin.bias)]
+    k1, b1, k2, b2, k3, b3, w, bl = ref_params
+    h = torch.relu(O.s2_convolution(x, k1, b1, 64, 16, g2))
+    h = torch.relu(O.so3_convolution(h, k2, b2, 16, 10, g3))
+    h = torch.relu(O.so3_convolution(h, k3, b3, 10, 5, g3))
+    logits_ref = torch.nn.functional.linear(O.so3_integrate(h), w, bl)
+    loss_ref = torch.nn.functional.cross_entropy(logits_ref, labels)
+    loss_ref.backward()
+
+    c1, c2, c3, lin = c1.to(dev), c2.to(dev), c3.to(dev), lin.to(dev)
+    h = torch.relu(c1(x.to(dev)))
+    h = torch.relu(c2(h))
+    h = torch.relu(c3(h))
+    logits = lin(S.so3_integrate(h))
+    loss = torch.nn.functional.cross_entropy(logits, labels.to(dev))
+    loss.backward()
+    assert_close(logits, logits_ref.detach(), "config 4 logits")
+    assert abs(loss.item() - loss_ref.item()) <= 1e-4 * max(1.0, abs(loss_ref.item()))
+    ours = [c1.kernel, c1.bias, c2.kernel, c2.bias, c3.kernel, c3.bias, lin.weight, lin.bias]
+    names = ["c1.kernel", "c1.bias", "c2.kernel", "c2.bias", "c3.kernel", "c3.bias", "lin.weight",
+             "lin.bias"]
+    for p, q, nm in zip(ours, ref_params, names):
+        assert_close(p.grad, q.grad, "config 4 grad " + nm)

@@ -47,14 +47,56 @@ def _worker(rank, world, port, tmp):
             y.backward(gy[lo:hi])
             n = parallel.allreduce_gradients(conv.parameters())
             assert n == conv.kernel.numel() + conv.bias.numel()
+            ref = S.SO3Convolution(2, 3, 4, 3, grid)
+            ref.load_state_dict(conv.state_dict())
+            yr = ref(x)
+            yr.backward(gy)
+            out = {"y": y.detach(), "yr": yr[lo:hi].detach(), "gk": conv.kernel.grad.clone(),
+                   "gkr": ref.kernel.grad, "gb": conv.bias.grad.clone(), "gbr": ref.bias.grad}
+
+            # a batch of ONE over two ranks: rank 1 owns nothing, runs no backward and must still
+            # take part in the collective with the same bucket layout (zeros), and receive the sum
+            conv.zero_grad(set_to_none=True)
+            lo1, hi1 = parallel.shard_range(1, rank, world)
+            if hi1 > lo1:
+                conv(x[lo1:hi1]).backward(gy[lo1:hi1])
+            else:
+                assert conv.kernel.grad is None
+            n = parallel.allreduce_gradients(conv.parameters())
+            assert n == conv.kernel.numel() + conv.bias.numel()
+            ref.zero_grad(set_to_none=True)
+            ref(x[:1]).backward(gy[:1])
+            out.update({"e_gk": conv.kernel.grad.clone(), "e_gkr": ref.kernel.grad.clone(),
+                        "e_gb": conv.bias.grad.clone(), "e_gbr": ref.bias.grad.clone()})
+
+            # the overlapped reducer (one bucket per layer, launched from autograd hooks) on a
+            # two-layer stack; second step with rank 1 skipping its backward pass entirely
+            torch.manual_seed(5)
+            net = torch.nn.Sequential(S.SO3Convolution(2, 3, 4, 3, grid), torch.nn.ReLU(),
+                                      S.SO3Convolution(3, 2, 3, 2, grid))
+            gy2 = torch.randn(5, 2, 4, 4, 4, generator=torch.Generator().manual_seed(3))
+            red = parallel.GradientReducer(net)
+            assert len(red.buckets) == 2
+            red.zero_grad()
+            net(x[lo:hi]).backward(gy2[lo:hi])
+            assert red.finish() == sum(p.numel() for p in net.parameters())
+            got = [p.grad.clone() for p in net.parameters()]
+            red.zero_grad()
             if rank == 0:
-                ref = S.SO3Convolution(2, 3, 4, 3, grid)
-                ref.load_state_dict(conv.state_dict())
-                yr = ref(x)
-                yr.backward(gy)
-                torch.save({"y": y.detach(), "yr": yr[lo:hi].detach(), "gk": conv.kernel.grad,
-                            "gkr": ref.kernel.grad, "gb": conv.bias.grad, "gbr": ref.bias.grad},
-                           os.path.join(tmp, "out.pt"))
+                net(x[:2]).backward(gy2[:2])
+            red.finish()
+            got2 = [p.grad.clone() for p in net.parameters()]
+            red.remove()
+            for p in net.parameters():
+                p.grad = None
+            net(x).backward(gy2)
+            want = [p.grad.clone() for p in net.parameters()]
+            for p in net.parameters():
+                p.grad = None
+            net(x[:2]).backward(gy2[:2])
+            want2 = [p.grad.clone() for p in net.parameters()]
+            out.update({"red": got, "red_ref": want, "red2": got2, "red2_ref": want2})
+            torch.save(out, os.path.join(tmp, "out%d.pt" % rank))
     finally:
         dist.destroy_process_group()
 
@@ -78,8 +120,15 @@ def test_two_ranks_match_single_process(tmp_path):
     emul.build()  # build once before forking workers
     port = _free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    out = torch.load(os.path.join(str(tmp_path), "out.pt"))
     from util import assert_close
-    assert_close(out["y"], out["yr"], "sharded forward")
-    assert_close(out["gk"], out["gkr"], "all-reduced kernel grad")
-    assert_close(out["gb"], out["gbr"], "all-reduced bias grad")
+    for rank in range(2):
+        out = torch.load(os.path.join(str(tmp_path), "out%d.pt" % rank))
+        assert_close(out["y"], out["yr"], "sharded forward")
+        assert_close(out["gk"], out["gkr"], "all-reduced kernel grad")
+        assert_close(out["gb"], out["gbr"], "all-reduced bias grad")
+        assert_close(out["e_gk"], out["e_gkr"], "kernel grad, rank with an empty shard")
+        assert_close(out["e_gb"], out["e_gbr"], "bias grad, rank with an empty shard")
+        for a, b in zip(out["red"], out["red_ref"]):
+            assert_close(a, b, "overlapped reducer, rank %d" % rank)
+        for a, b in zip(out["red2"], out["red2_ref"]):
+            assert_close(a, b, "overlapped reducer with an idle rank, rank %d" % rank)

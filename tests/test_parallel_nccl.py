@@ -1,5 +1,6 @@
 """The batch-sharded training step on real GPUs: two ranks over NCCL (127.0.0.1), each running the
-CUDA library on its half of the batch and reducing the parameter gradients with one all-reduce;
+CUDA library on its half of the batch and reducing the parameter gradients - once with one blocking
+all-reduce after backward, once with per-layer all-reduces launched from autograd hooks;
 rank 0 checks outputs and gradients against the unsharded step.  Skipped when fewer than two GPUs
 are visible (the CPU twin of this test is test_parallel_gloo.py)."""
 import os
@@ -56,13 +57,24 @@ def _worker(rank, world, port, tmp):
         n = parallel.allreduce_gradients(net.parameters())
         assert n == sum(p.numel() for p in net.parameters())
         torch.cuda.synchronize()
+        blocking = [p.grad.clone() for p in net.parameters()]
+        # the same step with the per-layer all-reduces launched from autograd hooks during backward
+        red = parallel.GradientReducer(net)
+        assert len(red.buckets) == 2
+        red.zero_grad()
+        forward(net, x[lo:hi]).backward(gy[lo:hi])
+        assert red.finish() == n
+        torch.cuda.synchronize()
+        overlapped = [p.grad.clone() for p in net.parameters()]
+        red.remove()
         if rank == 0:
             ref = make()
             yr = forward(ref, x)
             yr.backward(gy)
             out = {"y": y.detach().cpu(), "yr": yr[lo:hi].detach().cpu()}
-            for i, (p, q) in enumerate(zip(net.parameters(), ref.parameters())):
-                out["g%d" % i] = p.grad.cpu()
+            for i, q in enumerate(ref.parameters()):
+                out["g%d" % i] = blocking[i].cpu()
+                out["o%d" % i] = overlapped[i].cpu()
                 out["r%d" % i] = q.grad.cpu()
             torch.save(out, os.path.join(tmp, "out.pt"))
     finally:
@@ -81,5 +93,6 @@ def test_two_rank_training_step_over_nccl(tmp_path):
     i = 0
     while "g%d" % i in out:
         assert_close(out["g%d" % i], out["r%d" % i], "reduced gradient %d" % i)
+        assert_close(out["o%d" % i], out["r%d" % i], "gradient %d reduced from hooks" % i)
         i += 1
     assert i == 4
