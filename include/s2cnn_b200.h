@@ -224,10 +224,10 @@ int s2c_so3_rotate_spectrum(const float* U, const float* x, float* z, int b, lon
  *     kernels instead of the single-kernel path; 2 additionally replaces the plane kernels of
  *     2b = 64 / 128 (both row transforms of a (z, beta) plane in one kernel) by the three separate
  *     passes every other size uses; 0 restores the defaults.
- *   s2c_debug_plane_width(planes): plane kernels, 0 (default) = the fast variant, 1 = the simple
- *     variant that touches the scratch array directly. */
+ *   s2c_debug_plane_chunk(signals): signals per chunk of the large-bandwidth path (1 .. 8); 0
+ *     restores the default (8, or what the workspace holds). */
 void s2c_debug_force_general_path(int level);
-void s2c_debug_plane_width(int planes);
+void s2c_debug_plane_chunk(int signals);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,7 @@
 #include "so3_fused_kernels.h"
 #include "so3_relay_kernels.h"
 #include "wigner_tiled.h"
+#include "wigner_rows.h"
 #include "cgemm_kernels.h"
 #include "s2_mm_thin.h"
 #include "so3_mm_tc.h"
@@ -26,7 +27,7 @@ namespace s2c {
 thread_local long g_launch_count = 0;
 // test switches (process-wide, race-free; see the "test hooks" section of the header)
 static std::atomic<int> g_force_general{0};   // 1 = no single-kernel path, 2 = also no plane kernels
-static std::atomic<int> g_plane_width{0};     // plane kernels: 0 = fast variant, 1 = simple variant
+static std::atomic<int> g_plane_chunk{0};     // plane path: signals per chunk (0 = default)
 
 #define S2C_TRY(expr)            \
   do {                           \
@@ -52,27 +53,35 @@ static size_t so3_ws_per_z(int N, int K) {
 }
 static size_t s2_ws_per_z(int N, int K) { return (size_t)(2 * K - 1) * N * sizeof(float2); }
 
-static size_t so3_v_per_z(int N, int K) { return (size_t)K * (2 * K - 1) * N * sizeof(float2); }
-
-// Plane kernels (both row transforms of a (z, beta) plane in one kernel) for N = 64 and 128.
+// Large-bandwidth path for N = 64 and 128: a plane kernel (both row transforms of a (z, beta)
+// plane) and a Wigner kernel per direction, through the scratch array V[n][z][beta][f] of
+// 8 K N^2 bytes per signal, in chunks of at most kRowsZC signals so that V stays in L2 between the
+// two kernels (b = 64: 8.4 MB per signal, 67 MB per chunk of the 126 MB).
+static size_t so3_v_per_z(int N, int K) { return (size_t)K * N * N * sizeof(float2); }
 static bool use_plane_kernels(int N) { return plane_supported(N) && g_force_general < 2; }
+static long plane_chunk(long nbatch, size_t ws_bytes, int N, int K) {
+  const int want = g_plane_chunk.load();
+  long chunk = (want >= 1 && want <= kRowsZC) ? want : kRowsZC;
+  chunk = std::min<long>(chunk, (long)(ws_bytes / so3_v_per_z(N, K)));
+  return std::min(chunk, nbatch);
+}
 static int launch_fwd_plane(int N, long zc, stream_t st, const FwdPlaneParams& f) {
   const long grid = zc * N;
-  if (g_plane_width == 0) {
-    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 128, grid, st, f);
-    return S2C_LAUNCH_PLANE_CL(so3_fwd_plane, 64, grid, st, f);
-  }
   if (N == 128) return S2C_LAUNCH_PLANE(so3_fwd_plane, 128, grid, st, f);
   return S2C_LAUNCH_PLANE(so3_fwd_plane, 64, grid, st, f);
 }
 static int launch_inv_plane(int N, long zc, stream_t st, const InvPlaneParams& f) {
   const long grid = zc * N;
-  if (g_plane_width == 0) {
-    if (N == 128) return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 128, grid, st, f);
-    return S2C_LAUNCH_PLANE_CL(so3_inv_plane, 64, grid, st, f);
-  }
   if (N == 128) return S2C_LAUNCH_PLANE(so3_inv_plane, 128, grid, st, f);
   return S2C_LAUNCH_PLANE(so3_inv_plane, 64, grid, st, f);
+}
+static int launch_fwd_rows(int N, stream_t st, const FwdRowsParams& f) {
+  if (N == 128) return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 128, rows_grid(f.K), st, f);
+  return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 64, rows_grid(f.K), st, f);
+}
+static int launch_inv_rows(int N, stream_t st, const InvRowsParams& f) {
+  if (N == 128) return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 128, rows_grid(f.K), st, f);
+  return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 64, rows_grid(f.K), st, f);
 }
 
 static int check_b(int b_in, int b_out) {
@@ -116,7 +125,12 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
   const bool plane = use_plane_kernels(N);
-  if (plane) chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / so3_v_per_z(N, K));
+  HalfPanelsDev hp;
+  if (plane) {
+    chunk = plane_chunk(nbatch, ws_bytes, N, K);
+    hp.nbeta = N; hp.nl = b_out; hp.K = K; hp.npairs = pan.npairs;
+    S2C_TRY(TableCache::get().half_panels(b_in, b_out, K, weighted, &hp.data, &hp.off));
+  }
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     float2* u = (float2*)ws;
@@ -127,6 +141,11 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
       f.in_stride = in_stride; f.in_off = in_off;
       f.v = v; f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
       S2C_TRY(launch_fwd_plane(N, zc, st, f));
+      FwdRowsParams r;
+      r.v = v; r.out = out + z0; r.out_zstride = nbatch; r.pan = hp;
+      r.zc = (int)zc; r.K = K; r.nl = b_out; r.mode = mode;
+      S2C_TRY(launch_fwd_rows(N, st, r));
+      continue;
     } else {
     FwdGammaParams g;
     g.x = x + (size_t)z0 * N * N * N * in_stride;
@@ -232,11 +251,30 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
   const bool plane = use_plane_kernels(N);
-  if (plane) chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / so3_v_per_z(N, K));
+  HalfPanelsDev hp;
+  if (plane) {
+    chunk = plane_chunk(nbatch, ws_bytes, N, K);
+    hp.nbeta = N; hp.nl = K; hp.K = K; hp.npairs = pan.npairs;
+    S2C_TRY(TableCache::get().half_panels(b_out, K, K, weighted, &hp.data, &hp.off));
+  }
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     float2* t = (float2*)ws;                                   // [z][K][N][N]
     float2* s = plane ? t : t + (size_t)zc * K * N * N;        // [K][2K-1][z][N]
+    if (plane) {
+      InvRowsParams r;
+      r.x = x + z0; r.x_zstride = nbatch; r.s = s; r.pan = hp;
+      r.zc = (int)zc; r.K = K; r.mode = mode;
+      S2C_TRY(launch_inv_rows(N, st, r));
+      InvPlaneParams f;
+      f.s = s;
+      f.out = out + (size_t)z0 * N * N * N * out_stride;
+      f.out_stride = out_stride; f.out_off = out_off;
+      f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1; f.z0 = z0;
+      f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
+      S2C_TRY(launch_inv_plane(N, zc, st, f));
+      continue;
+    }
     InvWignerParams w;
     w.x = x + z0;
     w.x_zstride = nbatch;
@@ -254,16 +292,6 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     } else {
       const size_t wsm = align_up((size_t)K * N * sizeof(float), 16) + (size_t)K * w.ZT * sizeof(float2);
       S2C_TRY(S2C_LAUNCH(so3_inv_wigner, (long)pan.npairs * w.nzt, kThreads, wsm, st, w));
-    }
-    if (plane) {
-      InvPlaneParams f;
-      f.s = s;
-      f.out = out + (size_t)z0 * N * N * N * out_stride;
-      f.out_stride = out_stride; f.out_off = out_off;
-      f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1; f.z0 = z0;
-      f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
-      S2C_TRY(launch_inv_plane(N, zc, st, f));
-      continue;
     }
     InvAlphaParams a;
     a.s = s;
@@ -465,6 +493,13 @@ size_t s2c_so3_fft_workspace_min(int b_in, int b_out) {
 
 size_t s2c_so3_fft_workspace(long nbatch, int b_in, int b_out) {
   const size_t per_z = s2c_so3_fft_workspace_min(b_in, b_out);
+  if (plane_supported(2 * b_in) && plane_supported(2 * b_out)) {
+    // large-bandwidth path: one chunk of the scratch array V (sized to stay in L2); never less than
+    // one signal of the three-pass organisation, which the test switches can select instead
+    const int K = std::min(b_in, b_out);
+    const size_t v = std::max(so3_v_per_z(2 * b_in, K), so3_v_per_z(2 * b_out, K));
+    return std::max(per_z, v * (size_t)std::min<long>(kRowsZC, std::max(1L, nbatch)));
+  }
   const size_t target = (size_t)256 << 20;
   long chunk = (long)std::max<size_t>(32, target / per_z);
   chunk = std::min(chunk, std::max(1L, nbatch));
@@ -488,7 +523,7 @@ int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_o
 }
 
 void s2c_debug_force_general_path(int level) { g_force_general = level < 0 ? 0 : level; }
-void s2c_debug_plane_width(int planes) { g_plane_width = planes == 1 ? 1 : 0; }
+void s2c_debug_plane_chunk(int signals) { g_plane_chunk = signals < 0 ? 0 : signals; }
 
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                 void* ws, size_t ws_bytes, void* stream) {

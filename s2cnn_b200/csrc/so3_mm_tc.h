@@ -16,9 +16,10 @@
 // Precision: TF32 has 10 mantissa bits, not enough for the 1e-4 bar.  Every operand is split in
 // float32 into hi = v truncated to TF32 and lo = v - hi and three MMAs (hi*hi, lo*hi, hi*lo)
 // accumulate into the same float32 TMEM accumulator.  The tensor core's own accumulation
-// truncates, which shows after thousands of K steps (grad y contracts over (2l+1) * batch); every
-// kTcFlushBlocks K blocks the partial sum is therefore moved out of the MMA accumulator and added
-// in FP32 by the threads into a second TMEM region.
+// truncates - a bias of up to one unit in the last place per MMA, always in the same direction,
+// which adds up along the K loop.  The MMAs therefore alternate between two accumulators: every
+// kTcFlushBlocks K blocks the issuer switches to the other one, and while the tensor core fills
+// it the threads add the finished partial sum, rounding properly, into a third TMEM region.
 //
 // Tiling: one CTA per (l, 128-row tile, 128-column tile); the K loop walks the blocks (outer
 // contraction index, slice of its run of floats).  Operands are staged by all 512 threads into
@@ -83,9 +84,13 @@ constexpr int kTcBufBytes = (kTcKMax / 4) * kTcLBO;   // one operand buffer (hi 
 constexpr int kTcStageBytes = 4 * kTcBufBytes;        // A hi, A lo, B hi, B lo
 constexpr int kTcSmemBytes = 2 * kTcStageBytes + 64;
 constexpr int kTcThreads = 512;
-// K blocks accumulated in tensor memory before the partial sum moves to FP32 registers (bounds the
-// length of the tensor core's own accumulation chain, whose additions truncate)
-constexpr int kTcFlushBlocks = 16;
+// K blocks accumulated by the tensor core before the partial sum is added, in FP32 with rounding,
+// into the sum region (bounds the length of the tensor core's own accumulation chain, whose
+// additions truncate): 4 blocks = 72 MMAs per chain.
+constexpr int kTcFlushBlocks = 4;
+// tensor-memory columns: two alternating accumulators and the FP32 sum region (power of two)
+constexpr int kTcTmemCols = 512;
+constexpr int kTcSumCol = 2 * kTcBN;
 
 __device__ __forceinline__ uint32_t tc_smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -255,7 +260,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      tc_smem_u32(tmem_slot)),
-                 "r"(2 * kTcBN)
+                 "r"(kTcTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -371,9 +376,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     return odd ? make_float4(v.y, v.x, v.w, v.z) : make_float4(v.x, -v.y, v.z, -v.w);
   };
 
-  // This thread's share of the accumulator (TMEM lanes 32 (warp % 4) + lane, 32 columns).  Partial
-  // sums leave the MMA accumulator every kTcFlushBlocks K blocks and are added up in FP32 by the
-  // threads in a second tensor-memory region (columns kTcBN .. 2 kTcBN - 1).
+  // This thread's share of an accumulator (TMEM lanes 32 (warp % 4) + lane, 32 columns).  The
+  // accumulator of K-block group g is columns (g & 1) * kTcBN ...; the finished partial sum of a
+  // group is added in FP32 by the threads into the sum region (columns kTcSumCol ...) while the
+  // tensor core works on the next group in the other accumulator.
   constexpr int kColGroups = kTcThreads / 128;
   constexpr int kColsPerWarp = kTcBN / kColGroups;
   static_assert(kColsPerWarp == 32, "one tcgen05.ld of 32 columns per warp");
@@ -412,19 +418,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
       flush_parity ^= 1u;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
+      // the group that just ended: iteration it - 1, accumulator ((it - 1) / kTcFlushBlocks) & 1
+      const uint32_t done_acc = (uint32_t)((((it - 1) / kTcFlushBlocks) & 1) * kTcBN);
       for (int h = 0; h < 2; ++h) {       // 16 columns at a time keeps the transient registers low
         float v[16];
-        tc_ld16(tmem_mine + 16 * h, v);
+        tc_ld16(tmem_mine + done_acc + 16 * h, v);
         if (have_sum) {
           float w[16];
-          tc_ld16(tmem_mine + kTcBN + 16 * h, w);
+          tc_ld16(tmem_mine + kTcSumCol + 16 * h, w);
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] += w[i];
         }
-        tc_st16(tmem_mine + kTcBN + 16 * h, v);
+        tc_st16(tmem_mine + kTcSumCol + 16 * h, v);
       }
       have_sum = true;
-      // the block barrier below orders these reads before the MMA that restarts the accumulator
+      // that accumulator is written again kTcFlushBlocks iterations from now, after block barriers
+      // that every thread reaches only once these reads are done
     }
     if (it + 1 < nit) prefetch(it + 1);
     // make the generic-proxy writes visible to the tensor core (async proxy), then hand over
@@ -435,18 +444,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_hi = tc_smem_u32(Ahi), a_lo = tc_smem_u32(Alo);
       const uint32_t b_hi = tc_smem_u32(Bhi), b_lo = tc_smem_u32(Blo);
+      const uint32_t acc = tmem_base + (FLUSH ? (uint32_t)(((it / kTcFlushBlocks) & 1) * kTcBN) : 0u);
       for (int ks = 0; ks < ksteps; ++ks) {
         const uint32_t koff = (uint32_t)ks * 2u * kTcLBO;
         const uint64_t dah = tc_smem_desc(a_hi + koff), dal = tc_smem_desc(a_lo + koff);
         const uint64_t dbh = tc_smem_desc(b_hi + koff), dbl = tc_smem_desc(b_lo + koff);
-        tc_mma_tf32(tmem_base, dah, dbh, idesc, (fresh && ks == 0) ? 0u : 1u);
-        tc_mma_tf32(tmem_base, dal, dbh, idesc, 1u);
-        tc_mma_tf32(tmem_base, dah, dbl, idesc, 1u);
+        tc_mma_tf32(acc, dah, dbh, idesc, (fresh && ks == 0) ? 0u : 1u);
+        tc_mma_tf32(acc, dal, dbh, idesc, 1u);
+        tc_mma_tf32(acc, dah, dbl, idesc, 1u);
       }
       tc_commit(&mbar[s]);
     }
-    // every kTcFlushBlocks blocks the partial sum leaves the MMA accumulator (handled at the top
-    // of the next iteration, where the staging registers are free)
+    // every kTcFlushBlocks blocks the issuer moves on to the other accumulator; the finished
+    // partial sum is collected at the top of the next iteration, where the staging registers are free
     pending_flush = FLUSH && ((it + 1) % kTcFlushBlocks == 0) && (it + 1 < nit);
     fresh = pending_flush;
     if (pending_flush && tid == 0) tc_commit(flushbar);   // arrives when every MMA so far has finished
@@ -475,13 +485,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     // c[((spec0 + ro * sro + co * sco) * RI + ri) * CW + rem]
     const int sro = OP == kTcGradY ? 1 : L, sco = OP == kTcGradY ? L : 1;
 #pragma unroll 1
+    const uint32_t last_acc = FLUSH ? (uint32_t)((((nit - 1) / kTcFlushBlocks) & 1) * kTcBN) : 0u;
     for (int g = 0; g < kColsPerWarp / 32; ++g) {
       const int cbase = kColsPerWarp * cg + 32 * g;
       float v[32];
-      tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)cbase, v);
+      tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + last_acc + (uint32_t)cbase, v);
       if (FLUSH && have_sum) {
         float w[32];
-        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTcBN + cbase), w);
+        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTcSumCol + cbase), w);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] += w[i];
       }
@@ -529,7 +540,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   __syncthreads();
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(2 * kTcBN)
+                 "r"(kTcTmemCols)
                  : "memory");
   }
 }

@@ -242,6 +242,41 @@ class TableCache {
     return S2C_OK;
   }
 
+  // First half of the beta range of every SO(3) panel (rows of nbeta / 2 floats), for kernels that
+  // obtain the second half from d^l_{m,n}(pi - beta_j) = (-1)^(l+n) d^l_{-m,n}(beta_j) and the
+  // symmetry of the SOFT grid and its quadrature weights under beta -> pi - beta.  `off` holds
+  // npairs + 1 offsets in floats (pair order of so3_pair_index).
+  int half_panels(int b_beta, int nl, int K, bool weighted, const float** data,
+                  const long long** off) {
+    std::lock_guard<std::mutex> g(mu_);
+    const int dev = dev_current();
+    auto key = std::make_tuple(dev, b_beta, nl, K, (int)weighted, 0);
+    auto it = half_.find(key);
+    if (it == half_.end()) {
+      std::vector<float> full;
+      std::vector<long long> foff;
+      build_panels(b_beta, nl, K, weighted, false, full, foff);
+      const int nbeta = 2 * b_beta, nh = nbeta / 2;
+      std::vector<long long> hoff(foff.size());
+      for (size_t i = 0; i < foff.size(); ++i) hoff[i] = foff[i] / 2;
+      std::vector<float> half((size_t)hoff.back());
+      const long long nrows = foff.back() / nbeta;
+      for (long long r = 0; r < nrows; ++r)
+        std::copy(full.begin() + r * nbeta, full.begin() + r * nbeta + nh, half.begin() + r * nh);
+      void* dd = dev_alloc(half.size() * sizeof(float));
+      void* doff = dev_alloc(hoff.size() * sizeof(long long));
+      if (!dd || !doff) return fail(S2C_ERR_CUDA, "table allocation failed");
+      int rc = dev_upload(dd, half.data(), half.size() * sizeof(float));
+      if (rc) return rc;
+      rc = dev_upload(doff, hoff.data(), hoff.size() * sizeof(long long));
+      if (rc) return rc;
+      it = half_.emplace(key, std::make_pair((const float*)dd, (const long long*)doff)).first;
+    }
+    *data = it->second.first;
+    *off = it->second.second;
+    return S2C_OK;
+  }
+
   int quad_weights(int b, const float** out) {
     std::lock_guard<std::mutex> g(mu_);
     const int dev = dev_current();
@@ -272,6 +307,8 @@ class TableCache {
     }
     for (auto& kv : quad_) dev_free((void*)kv.second);
     for (auto& kv : grouped_) dev_free((void*)kv.second.first);
+    for (auto& kv : half_) { dev_free((void*)kv.second.first); dev_free((void*)kv.second.second); }
+    half_.clear();
     grouped_.clear();
     fft_.clear();
     panels_.clear();
@@ -284,6 +321,7 @@ class TableCache {
   std::map<std::tuple<int, int, int, int, int, int>, PanelsDev> panels_;
   std::map<std::pair<int, int>, const float*> quad_;
   std::map<std::tuple<int, int, int, int, int, int>, std::pair<const float*, int>> grouped_;
+  std::map<std::tuple<int, int, int, int, int, int>, std::pair<const float*, const long long*>> half_;
 };
 
 }  // namespace s2c

@@ -1,0 +1,528 @@
+// Wigner-d contractions of the large-bandwidth SO(3) path (N = 2b in {64, 128}), written for SMALL
+// batch chunks: the scratch array V between the plane kernels (so3_plane_kernels.h) and these
+// kernels must stay in L2, so a launch sees only a handful of signals and a tile that reuses a
+// staged Wigner panel over many batch elements (wigner_tiled.h) has nothing to reuse it over.
+//
+// Same arithmetic as so3_fwd_wigner / so3_inv_wigner (so3_kernels.h), i.e. the beta / l contraction
+// of the reference's so3fft.cu / so3ifft.cu tile loops (s2cnn/soft/so3_fft.py:296-336, :391-431).
+//
+// Organisation: the 32 lanes of a warp split the BETA axis; a warp owns the frequency pair
+// (+m, n) and (-m, n) for four batch elements, a block of 8 warps four values of |m| times two
+// groups of four batch elements.
+//   * The table holds only the first half of the beta range (TableCache::half_panels): the
+//     SOFT grid maps onto itself under beta -> pi - beta and
+//         d^l_{m,n}(pi - beta_j) = (-1)^(l+n) d^l_{-m,n}(beta_j),
+//     so the second half of panel (m, n) is the first half of panel (-m, n) up to that sign.  A warp
+//     reads row l of both half panels once - 2 x N/2 consecutive floats, one coalesced load per
+//     lane - and uses each for both members of its pair.
+//   * analysis: the warp keeps its slice of V in registers for the whole pair and streams the
+//     panel rows; every degree ends with a sum over the lanes (a 32-value transpose-reduce by
+//     shuffles for two degrees at a time, after which lane i holds value i).
+//   * synthesis: the accumulators (one beta slice of four signals per lane) stay in registers
+//     while the rows stream; no cross-lane traffic at all.
+//   * V is [n][z][beta][f] (f = alpha-frequency bin, see so3_plane_kernels.h): the block moves its
+//     8 columns (+-m) between global and shared memory one 32-byte sector per (z, beta) at a time and
+//     the lanes read / write the transposed tile [column][z][beta] without bank conflicts.
+#pragma once
+
+#include "backend.h"
+#include "so3_kernels.h"
+
+namespace s2c {
+
+constexpr int kRowsMG = 4;      // values of |m| per block
+constexpr int kRowsZH = 4;      // batch elements per warp
+constexpr int kRowsZC = 8;      // batch elements per block = chunk size the host uses
+constexpr int kRowsThreads = 32 * kRowsMG * (kRowsZC / kRowsZH);
+
+struct HalfPanelsDev {
+  int nbeta;                // N = 2 b of the beta grid
+  int nl, K, npairs;
+  const float* data;        // per pair: rows l = lmin .. nl-1, N/2 floats each (beta_j, j < N/2)
+  const long long* off;     // npairs + 1 offsets in floats
+};
+
+struct FwdRowsParams {
+  const float2* v;      // [n < K][z < zc][beta][f]
+  float2* out;          // spectrum rows of out_zstride complex, already offset to the chunk's z0
+  long out_zstride;
+  HalfPanelsDev pan;
+  int zc, K, nl, mode;  // mode: kSo3Real or kSo3AccumI
+};
+
+struct InvRowsParams {
+  const float2* x;      // spectrum rows of x_zstride complex, offset to the chunk's z0
+  long x_zstride;
+  float2* s;            // [n < K][z < zc][beta][f]
+  HalfPanelsDev pan;
+  int zc, K, mode;      // mode: kSo3Real or kSo3RotI
+};
+
+// Panel rows reach a warp through a private ring of kRowsDepth steps in shared memory, filled by
+// asynchronous copies (cp.async): every lane copies and later reads only its own beta slice, so
+// the ring needs no barrier, only the per-thread wait for the oldest copy group - and the rows of
+// the next kRowsDepth steps are in flight while the current one is being used (with one
+// outstanding row per warp the kernels ran at the latency, not the bandwidth, of L2 / HBM).
+constexpr int kRowsDepth = 8;
+
+// shared memory: the tile [8 columns][zc = 8][N beta] of complex numbers.  The rings [warp][depth]
+// [rows per step][A, B][N / 2] live inside it: the analysis is done with the tile once every warp
+// has its slice of V in registers (whole tile = 8 rings of depth 8 x 2 rows), the synthesis keeps
+// the symmetrised spectrum rows in the lower half until the tile is written and its rings (depth 8
+// x 1 row) in the upper half.  (+ in the host-emulation build a per-warp exchange buffer that
+// stands in for the shuffles.)
+template <int N>
+S2C_HD constexpr int rows_tile_floats() { return 2 * kRowsMG * kRowsZC * N * 2; }
+template <int N>
+S2C_HD constexpr int rows_ring_floats(int rows_per_step) { return kRowsDepth * rows_per_step * 2 * (N / 2); }
+template <int N>
+inline size_t rows_smem_bytes() {
+  static_assert((kRowsThreads / 32) * rows_ring_floats<N>(2) <= rows_tile_floats<N>(), "analysis rings");
+  static_assert((kRowsThreads / 32) * rows_ring_floats<N>(1) <= rows_tile_floats<N>() / 2, "synthesis rings");
+  size_t b = (size_t)rows_tile_floats<N>() * sizeof(float);
+#ifdef S2C_EMUL
+  b += (size_t)(kRowsThreads / 32) * 32 * 33 * sizeof(float);
+#endif
+  return b;
+}
+
+// JL consecutive floats global -> shared, asynchronously; groups complete in issue order
+#ifndef S2C_EMUL
+template <int JL>
+S2C_D void rows_copy_async(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(dst)), "l"(src),
+               "n"(JL * 4)
+               : "memory");
+}
+S2C_D void rows_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// kRowsDepth - 1 steps are in flight: wait until at most kRowsDepth - 2 of this thread's copy
+// groups are pending, i.e. the oldest has landed.  (The step issued next goes into the slot that
+// was read one iteration earlier, never into the one being read.)
+S2C_D void rows_wait_oldest() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(kRowsDepth - 2) : "memory");
+}
+#else
+template <int JL>
+inline void rows_copy_async(float* dst, const float* src) {
+  for (int i = 0; i < JL; ++i) dst[i] = src[i];
+}
+inline void rows_commit() {}
+inline void rows_wait_oldest() {}
+#endif
+
+// ---- sum over the lanes of a warp: v[i] of every lane -> lane i -------------------------------
+#ifndef S2C_EMUL
+S2C_D float rows_reduce32(const Ctx&, float (&v)[32], int lane, float*) {
+#pragma unroll
+  for (int step = 16; step >= 1; step >>= 1) {
+    const bool upper = (lane & step) != 0;
+#pragma unroll
+    for (int k = 0; k < step; ++k) {
+      const float send = upper ? v[k] : v[k + step];
+      const float keep = upper ? v[k + step] : v[k];
+      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+    }
+  }
+  return v[0];
+}
+S2C_D float rows_partner(const Ctx&, float v, int, float*) {
+  return __shfl_xor_sync(0xffffffffu, v, 1);
+}
+#else
+// every warp of the block calls these equally often (a warp barrier is a block barrier here)
+inline float rows_reduce32(const Ctx& ctx, float (&v)[32], int lane, float* xch) {
+  for (int k = 0; k < 32; ++k) xch[lane * 33 + k] = v[k];
+  ctx.sync_warp();
+  float s = 0.f;
+  for (int t = 0; t < 32; ++t) s += xch[t * 33 + lane];
+  ctx.sync_warp();
+  return s;
+}
+inline float rows_partner(const Ctx& ctx, float v, int lane, float* xch) {
+  xch[lane] = v;
+  ctx.sync_warp();
+  const float r = xch[lane ^ 1];
+  ctx.sync_warp();
+  return r;
+}
+#endif
+
+// which (n, |m| group) a block owns, and the columns of its tile:
+//   c < kRowsMG:  frequency +(m0 + c)  at bin f = m0 + c
+//   c >= kRowsMG: frequency -(m0 + c - kRowsMG) at bin f = N - (m0 + c - kRowsMG)   (not for m = 0)
+struct RowsGeom {
+  int n, m0;
+};
+S2C_D RowsGeom rows_geom(int bid, int K) {
+  const int ngroups = (K + kRowsMG - 1) / kRowsMG;
+  RowsGeom g;
+  g.n = bid / ngroups;
+  g.m0 = (bid - g.n * ngroups) * kRowsMG;
+  return g;
+}
+inline long rows_grid(int K) { return (long)K * ((K + kRowsMG - 1) / kRowsMG); }
+
+// half-panel rows of the pair (+m, n) and (-m, n); for n = 0 only m >= 0 is stored and
+// d_{-m,0} = (-1)^m d_{m,0}; for m = 0 the two coincide
+struct RowsPanels {
+  const float* a;      // half panel of (+m, n)
+  const float* b;      // half panel of (-m, n) (or of (+m, n) with `bsign`)
+  float bsign;
+};
+S2C_D RowsPanels rows_panels(const HalfPanelsDev& pan, int m, int n) {
+  RowsPanels r;
+  r.a = pan.data + pan.off[so3_pair_index(m, n, pan.K)];
+  if (n == 0 || m == 0) {
+    r.b = r.a;
+    r.bsign = (n == 0 && (m & 1)) ? -1.f : 1.f;
+  } else {
+    r.b = pan.data + pan.off[so3_pair_index(-m, n, pan.K)];
+    r.bsign = 1.f;
+  }
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// analysis:  X[l, +-m, n][z] = sum_beta W[l][beta] V[z][beta]   (+ Hermitian mirror rows)
+// ---------------------------------------------------------------------------------------------
+template <int N>
+struct so3_fwd_wigner_r_impl {
+  static S2C_D void run(const Ctx& ctx, const FwdRowsParams& p, unsigned char* smem) {
+    constexpr int NH = N / 2, JL = NH / 32;           // betas of the half range per lane
+    constexpr int ZS = N, CS = kRowsZC * N;           // tile strides (complex): z, column
+    float2* tile = reinterpret_cast<float2*>(smem);   // [2 MG][ZC][N]
+    const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
+    // ring step = two degrees: [depth][row 0 / 1][A / B][NH]; reuses the tile's memory (see below)
+    float* ring = reinterpret_cast<float*>(smem) + warp * rows_ring_floats<N>(2);
+    float* xch = reinterpret_cast<float*>(smem) + rows_tile_floats<N>() + warp * 32 * 33;
+    const RowsGeom g = rows_geom(ctx.bid, p.K);
+    const int n = g.n, m0 = g.m0, K = p.K, zc = p.zc;
+
+    // ---- stage the block's columns of V: tile[c][z][beta] ----------------------------------------
+    // (z, beta) rows are 8 N bytes apart in V, so every load is a sector of its own; all loads of a
+    // thread are issued before the first value is used
+    {
+      constexpr int kIt = kRowsZC * N / kRowsThreads;   // rows per thread
+      static_assert(kRowsZC * N % kRowsThreads == 0, "tile rows per thread");
+      const float2* vn = p.v + (long)n * zc * N * N;
+      float4 p0[kIt], p1[kIt];
+      float2 ng[kIt][kRowsMG];
+#pragma unroll
+      for (int k = 0; k < kIt; ++k) {
+        const int it = ctx.tid + k * kRowsThreads;
+        const int z = it / N, beta = it - z * N;
+        p0[k] = p1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < kRowsMG; ++c) ng[k][c] = make_float2(0.f, 0.f);
+        if (z < zc) {
+          const float2* row = vn + ((long)z * N + beta) * N;
+          p0[k] = *reinterpret_cast<const float4*>(row + m0);
+          p1[k] = *reinterpret_cast<const float4*>(row + m0 + 2);
+#pragma unroll
+          for (int c = 0; c < kRowsMG; ++c)
+            if (m0 + c > 0) ng[k][c] = row[N - m0 - c];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kIt; ++k) {
+        const int it = ctx.tid + k * kRowsThreads;
+        const int z = it / N, beta = it - z * N;
+        float2* dst = tile + z * ZS + beta;
+        dst[0 * CS] = make_float2(p0[k].x, p0[k].y);
+        dst[1 * CS] = make_float2(p0[k].z, p0[k].w);
+        dst[2 * CS] = make_float2(p1[k].x, p1[k].y);
+        dst[3 * CS] = make_float2(p1[k].z, p1[k].w);
+#pragma unroll
+        for (int c = 0; c < kRowsMG; ++c) dst[(kRowsMG + c) * CS] = ng[k][c];
+      }
+    }
+    ctx.sync();
+
+    const int mi = warp % kRowsMG, zh = warp / kRowsMG;
+    const int m = m0 + mi;
+    const int lmin = m > n ? m : n;
+    const int L = (m < K) ? p.nl - lmin : 0;
+#ifdef S2C_EMUL
+    const int lmin_blk = m0 > n ? m0 : n;
+    const int Lloop = p.nl - lmin_blk > 0 ? p.nl - lmin_blk : 0;   // uniform over the block
+#else
+    const int Lloop = L;
+#endif
+
+    // ---- this lane's slice of V: betas j (p) and N-1-j (q) of the columns +m and -m ----------------
+    float2 vp[2][kRowsZH][JL], vq[2][kRowsZH][JL];
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int z = 0; z < kRowsZH; ++z)
+#pragma unroll
+        for (int jj = 0; jj < JL; ++jj) {
+          const int j = JL * lane + jj;
+          const float2* col = tile + (s * kRowsMG + mi) * CS + (zh * kRowsZH + z) * ZS;
+          vp[s][z][jj] = col[j];
+          vq[s][z][jj] = col[N - 1 - j];
+        }
+
+    RowsPanels pn;
+    pn.a = pn.b = p.pan.data;
+    pn.bsign = 1.f;
+    if (L > 0) pn = rows_panels(p.pan, m, n);
+    const bool self = (m == 0);
+    const float* pa = pn.a + JL * lane;
+    const float* pb = pn.b + JL * lane;
+    ctx.sync();   // every warp has its slice of V in registers: the tile's memory becomes the rings
+
+    // step t of the ring holds rows 2t and 2t + 1 (this lane's JL betas of each)
+    auto issue = [&](int t) {
+      float* slot = ring + (t % kRowsDepth) * (4 * NH) + JL * lane;
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+        if (2 * t + r < L) {
+          rows_copy_async<JL>(slot + (2 * r) * NH, pa + (long)(2 * t + r) * NH);
+          rows_copy_async<JL>(slot + (2 * r + 1) * NH, pb + (long)(2 * t + r) * NH);
+        }
+      rows_commit();   // one group per step, empty or not, so that the wait below counts steps
+    };
+#ifndef S2C_EMUL
+    if (L <= 0) return;   // no block barrier below this point
+#endif
+    for (int t = 0; t < kRowsDepth - 1; ++t) issue(t);
+
+    float va[2][JL], vb[2][JL];     // rows li, li + 1 of the two half panels
+    const int z0h = zh * kRowsZH;
+    for (int li = 0; li < Lloop; li += 2) {
+      rows_wait_oldest();
+      {
+        const float* slot = ring + ((li / 2) % kRowsDepth) * (4 * NH) + JL * lane;
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int jj = 0; jj < JL; ++jj) {
+            const bool ok = li + r < L;
+            va[r][jj] = ok ? slot[(2 * r) * NH + jj] : 0.f;
+            vb[r][jj] = ok ? pn.bsign * slot[(2 * r + 1) * NH + jj] : 0.f;
+          }
+      }
+      issue(li / 2 + kRowsDepth - 1);
+      float val[32];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int l = lmin + li + r;
+        const float sl = ((l + n) & 1) ? -1.f : 1.f;
+#pragma unroll
+        for (int z = 0; z < kRowsZH; ++z) {
+          float pr = 0.f, pi = 0.f, qr = 0.f, qi = 0.f;
+#pragma unroll
+          for (int jj = 0; jj < JL; ++jj) {
+            const float a = va[r][jj], b = vb[r][jj], sa = sl * a, sb = sl * b;
+            // X_{+m} = sum A Vp_{+m} + s B Vq_{+m};   X_{-m} = sum B Vp_{-m} + s A Vq_{-m}
+            pr = fmaf(a, vp[0][z][jj].x, pr);  pi = fmaf(a, vp[0][z][jj].y, pi);
+            pr = fmaf(sb, vq[0][z][jj].x, pr); pi = fmaf(sb, vq[0][z][jj].y, pi);
+            qr = fmaf(b, vp[1][z][jj].x, qr);  qi = fmaf(b, vp[1][z][jj].y, qi);
+            qr = fmaf(sa, vq[1][z][jj].x, qr); qi = fmaf(sa, vq[1][z][jj].y, qi);
+          }
+          val[r * 16 + 0 * 8 + z * 2 + 0] = pr;
+          val[r * 16 + 0 * 8 + z * 2 + 1] = pi;
+          val[r * 16 + 1 * 8 + z * 2 + 0] = qr;
+          val[r * 16 + 1 * 8 + z * 2 + 1] = qi;
+        }
+      }
+      const float mine = rows_reduce32(ctx, val, lane, xch);   // value `lane` summed over the warp
+      const float other = rows_partner(ctx, mine, lane, xch);  // the other component of the number
+      // lane = r * 16 + s * 8 + z * 2 + c
+      const int r = lane >> 4, s = (lane >> 3) & 1, z = (lane >> 1) & 3, c = lane & 1;
+      const int l = lmin + li + r, zz = z0h + z;
+      if (li + r < L && zz < zc && !(self && s == 1)) {
+        const int mm = s ? -m : m;
+        float* o1 = reinterpret_cast<float*>(p.out + so3_row(l, mm, n) * p.out_zstride + zz) + c;
+        const float fudge = ((mm - n) & 1) ? -1.f : 1.f;
+        const bool mirror = n > 0;      // for n = 0 the mirror (-m, 0) is computed directly
+        float* o2 = reinterpret_cast<float*>(p.out + so3_row(l, -mm, -n) * p.out_zstride + zz) + c;
+        if (p.mode == kSo3Real) {
+          *o1 = mine;
+          if (mirror) *o2 = c ? -fudge * mine : fudge * mine;
+        } else {   // += i * (re + i im):  re -= im, im += re;   mirror += i * fudge * conj
+          *o1 += c ? other : -other;
+          if (mirror) *o2 += fudge * other;
+        }
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// synthesis:  S[z][beta] = sum_l W[l][beta] Xs[l][z],  Xs = symmetrised spectrum
+// ---------------------------------------------------------------------------------------------
+template <int N>
+struct so3_inv_wigner_r_impl {
+  static S2C_D void run(const Ctx& ctx, const InvRowsParams& p, unsigned char* smem) {
+    constexpr int NH = N / 2, JL = NH / 32;
+    constexpr int ZS = N, CS = kRowsZC * N;
+    float2* tile = reinterpret_cast<float2*>(smem);     // [2 MG][ZC][N], written after the loop
+    float2* xs = tile;                                    // before: [2 MG][Lmax][ZC] symmetrised rows
+    const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
+    // ring step = one degree: [depth][A / B][NH], in the upper half of the tile's memory
+    float* ring = reinterpret_cast<float*>(smem) + rows_tile_floats<N>() / 2 + warp * rows_ring_floats<N>(1);
+    const RowsGeom g = rows_geom(ctx.bid, p.K);
+    const int n = g.n, m0 = g.m0, K = p.K, zc = p.zc, nl = p.pan.nl;
+    const int lmin_blk = m0 > n ? m0 : n;
+    const int Lmax = nl - lmin_blk;                      // rows of the block's longest pair (<= N/2)
+
+    // ---- symmetrised spectrum rows of the block's 8 columns: xs[c][li][z], li from lmin_blk -------
+    // thread = (z, li mod 32); the loads of all 8 columns are issued before any is used
+    {
+      const int z = ctx.tid % kRowsZC;
+      for (int li = ctx.tid / kRowsZC; li < Lmax; li += kRowsThreads / kRowsZC) {
+        const int l = lmin_blk + li;
+        float2 a[2 * kRowsMG], b[2 * kRowsMG];
+        bool ok[2 * kRowsMG];
+#pragma unroll
+        for (int c = 0; c < 2 * kRowsMG; ++c) {
+          const int mabs = m0 + (c % kRowsMG);
+          const int mm = c < kRowsMG ? mabs : -mabs;
+          ok[c] = z < zc && mabs < K && l >= mabs && !(c >= kRowsMG && mabs == 0);
+          a[c] = b[c] = make_float2(0.f, 0.f);
+          if (ok[c]) {
+            a[c] = p.x[so3_row(l, mm, n) * p.x_zstride + z];
+            b[c] = p.x[so3_row(l, -mm, -n) * p.x_zstride + z];
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 2 * kRowsMG; ++c) {
+          const int mabs = m0 + (c % kRowsMG);
+          const int mm = c < kRowsMG ? mabs : -mabs;
+          float2 u = a[c], w = b[c];
+          if (p.mode == kSo3RotI) {  // multiply the spectrum by -i
+            u = make_float2(u.y, -u.x);
+            w = make_float2(w.y, -w.x);
+          }
+          const float fudge = ((mm - n) & 1) ? -1.f : 1.f;
+          xs[(c * Lmax + li) * kRowsZC + z] =
+              make_float2(0.5f * (u.x + fudge * w.x), 0.5f * (u.y - fudge * w.y));
+        }
+      }
+    }
+    ctx.sync();
+
+    const int mi = warp % kRowsMG, zh = warp / kRowsMG;
+    const int m = m0 + mi;
+    const int lmin = m > n ? m : n;
+    const int L = (m < K) ? nl - lmin : 0;
+    const bool self = (m == 0);
+
+    // accumulators: betas j (p) and N-1-j (q) of the columns +m (0) and -m (1)
+    float2 sp[2][kRowsZH][JL], sq[2][kRowsZH][JL];
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int z = 0; z < kRowsZH; ++z)
+#pragma unroll
+        for (int jj = 0; jj < JL; ++jj) sp[s][z][jj] = sq[s][z][jj] = make_float2(0.f, 0.f);
+
+    if (L > 0) {
+      const RowsPanels pn = rows_panels(p.pan, m, n);
+      const float* pa = pn.a + JL * lane;
+      const float* pb = pn.b + JL * lane;
+      const float2* x0 = xs + ((0 * kRowsMG + mi) * Lmax + (lmin - lmin_blk)) * kRowsZC + zh * kRowsZH;
+      const float2* x1 = xs + ((1 * kRowsMG + mi) * Lmax + (lmin - lmin_blk)) * kRowsZC + zh * kRowsZH;
+      auto issue = [&](int t) {
+        float* slot = ring + (t % kRowsDepth) * (2 * NH) + JL * lane;
+        if (t < L) {
+          rows_copy_async<JL>(slot, pa + (long)t * NH);
+          rows_copy_async<JL>(slot + NH, pb + (long)t * NH);
+        }
+        rows_commit();
+      };
+      for (int t = 0; t < kRowsDepth - 1; ++t) issue(t);
+      float a[JL], b[JL];
+      for (int li = 0; li < L; ++li) {
+        rows_wait_oldest();
+        {
+          const float* slot = ring + (li % kRowsDepth) * (2 * NH) + JL * lane;
+#pragma unroll
+          for (int jj = 0; jj < JL; ++jj) { a[jj] = slot[jj]; b[jj] = pn.bsign * slot[NH + jj]; }
+        }
+        issue(li + kRowsDepth - 1);
+        const int l = lmin + li;
+        const float sl = ((l + n) & 1) ? -1.f : 1.f;
+#pragma unroll
+        for (int z = 0; z < kRowsZH; ++z) {
+          const float2 xp = x0[li * kRowsZC + z], xm = x1[li * kRowsZC + z];
+#pragma unroll
+          for (int jj = 0; jj < JL; ++jj) {
+            const float sa = sl * a[jj], sb = sl * b[jj];
+            // S_{+m}[j] += A X_{+m};  S_{+m}[N-1-j] += s B X_{+m};  S_{-m}[j] += B X_{-m};  S_{-m}[N-1-j] += s A X_{-m}
+            sp[0][z][jj].x = fmaf(a[jj], xp.x, sp[0][z][jj].x); sp[0][z][jj].y = fmaf(a[jj], xp.y, sp[0][z][jj].y);
+            sq[0][z][jj].x = fmaf(sb, xp.x, sq[0][z][jj].x);    sq[0][z][jj].y = fmaf(sb, xp.y, sq[0][z][jj].y);
+            sp[1][z][jj].x = fmaf(b[jj], xm.x, sp[1][z][jj].x); sp[1][z][jj].y = fmaf(b[jj], xm.y, sp[1][z][jj].y);
+            sq[1][z][jj].x = fmaf(sa, xm.x, sq[1][z][jj].x);    sq[1][z][jj].y = fmaf(sa, xm.y, sq[1][z][jj].y);
+          }
+        }
+      }
+    }
+    ctx.sync();   // every warp is done with the spectrum rows; the same memory becomes the tile
+
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int z = 0; z < kRowsZH; ++z)
+#pragma unroll
+        for (int jj = 0; jj < JL; ++jj) {
+          const int j = JL * lane + jj;
+          float2* col = tile + (s * kRowsMG + mi) * CS + (zh * kRowsZH + z) * ZS;
+          col[j] = sp[s][z][jj];
+          col[N - 1 - j] = sq[s][z][jj];
+        }
+    ctx.sync();
+
+    // ---- tile -> V[n][z][beta][f]: bins m0 .. m0+3 as one sector, bins N - m singly -----------------
+    {
+      float2* vn = p.s + (long)n * zc * N * N;
+      for (int it = ctx.tid; it < kRowsZC * N; it += ctx.nthr) {
+        const int z = it / N, beta = it - z * N;
+        if (z >= zc) continue;
+        const float2* src = tile + z * ZS + beta;
+        float2* row = vn + ((long)z * N + beta) * N;
+        const float2 c0 = src[0 * CS], c1 = src[1 * CS], c2 = src[2 * CS], c3 = src[3 * CS];
+        if (m0 + 3 < K) {
+          *reinterpret_cast<float4*>(row + m0) = make_float4(c0.x, c0.y, c1.x, c1.y);
+          *reinterpret_cast<float4*>(row + m0 + 2) = make_float4(c2.x, c2.y, c3.x, c3.y);
+        } else {
+          if (m0 < K) row[m0] = c0;
+          if (m0 + 1 < K) row[m0 + 1] = c1;
+          if (m0 + 2 < K) row[m0 + 2] = c2;
+        }
+#pragma unroll
+        for (int c = 0; c < kRowsMG; ++c) {
+          const int mm = m0 + c;
+          if (mm > 0 && mm < K) row[N - mm] = src[(kRowsMG + c) * CS];
+        }
+      }
+    }
+    (void)self;
+  }
+};
+
+#ifndef S2C_EMUL
+template <int N>
+__global__ void __launch_bounds__(kRowsThreads, 2) so3_fwd_wigner_r(const FwdRowsParams p) {
+  extern __shared__ float4 s2c_dyn_smem[];
+  Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
+  so3_fwd_wigner_r_impl<N>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+}
+template <int N>
+__global__ void __launch_bounds__(kRowsThreads, 2) so3_inv_wigner_r(const InvRowsParams p) {
+  extern __shared__ float4 s2c_dyn_smem[];
+  Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
+  so3_inv_wigner_r_impl<N>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
+}
+#define S2C_LAUNCH_ROWS(name, N, grid, stream, params)                                         \
+  s2c::launch_impl(name<N>, #name, (long)(grid), s2c::kRowsThreads, s2c::rows_smem_bytes<N>(), \
+                   stream, params)
+#else
+#define S2C_LAUNCH_ROWS(name, N, grid, stream, params)                                         \
+  s2c::emu_launch<name##_impl<N>>(#name, (long)(grid), s2c::kRowsThreads,                      \
+                                  s2c::rows_smem_bytes<N>(), params)
+#endif
+
+}  // namespace s2c

@@ -6,10 +6,14 @@ raw pointers plus the current CUDA stream.  The public, reference-named API in t
 is built on ``cuda_ops()``, which is bound to the CUDA build and refuses CPU tensors.
 """
 import contextlib
+import os
 
 import torch
 
 from . import _lib
+
+
+_CHECK_TC = bool(os.environ.get("S2CNN_B200_CHECK_TC"))
 
 
 def so3_nspec(b):
@@ -283,7 +287,19 @@ class Ops:
         with self._ctx(a):
             self.lib.call(fn, a.data_ptr(), b.data_ptr(), out.data_ptr(), nl, nbatch, f_in, f_out,
                           self._stream(a))
+            if _CHECK_TC and self.lib.is_cuda:
+                self.check_tensor_core_status()
         return out
+
+    def check_tensor_core_status(self):
+        """Waits for the device and raises if a tensor-core product has given up on one of its
+        bounded barrier waits since the library was loaded (its output is then undefined).  Called
+        after every spectral product when the environment variable S2CNN_B200_CHECK_TC is set; a
+        training loop can call it once per step instead."""
+        rc = self.lib.s2c_so3_mm_tc_status()
+        if rc != 0:
+            raise _lib.S2cError("s2cnn_b200: a tensor-core spectral product reported a barrier "
+                                "time-out (status %d); its results are invalid" % rc)
 
     @staticmethod
     def _mm_dims(x_shape, y_shape, so3):

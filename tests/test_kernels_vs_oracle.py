@@ -400,11 +400,11 @@ def test_general_path_tiled_wigner_odd_batches(backend, b_in, b_out, nbatch):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
-@pytest.mark.parametrize("b_in,b_out,nbatch", [(32, 32, 1), (32, 9, 2), (10, 32, 2)])
+@pytest.mark.parametrize("b_in,b_out,nbatch", [(32, 32, 1), (32, 9, 3), (10, 32, 2), (32, 34, 2)])
 def test_bandwidth_32_two_step_fft(backend, b_in, b_out, nbatch):
-    """2b = 64: the plane kernels (both row transforms of a (z, beta) plane in one kernel; with and
-    without the cluster exchange on the GPU) and the three separate passes with the two-step
-    register FFT (8 x 8) must all agree with the oracle."""
+    """2b = 64: the large-bandwidth path (plane kernels + the lanes-over-beta Wigner kernels, whole
+    batch in one chunk and one or two signals per chunk) and the three separate passes with the
+    two-step register FFT (8 x 8) must all agree with the oracle."""
     ops, dev = backends.get(backend)
     gen = torch.Generator().manual_seed(b_in + b_out)
     x = torch.randn(nbatch, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen)
@@ -414,14 +414,14 @@ def test_bandwidth_32_two_step_fft(backend, b_in, b_out, nbatch):
     ref_f, ref_i = O.so3_rfft(x, False, b_out), O.so3_rifft(s, False, b_out)
     ref_c, ref_ic = O.so3_fft(xc, True, b_out), O.so3_ifft(s, True, b_out)
     try:
-        for level, width in ((0, 0), (0, 1), (2, 0)):
+        for level, width in ((0, 0), (0, 2 if nbatch > 2 else 1), (2, 0)):
             ops.lib.s2c_debug_force_general_path(level)
-            ops.lib.s2c_debug_plane_width(width)
-            tag = " level %d width %d" % (level, width)
+            ops.lib.s2c_debug_plane_chunk(width)
+            tag = " level %d chunk %d" % (level, width)
             assert_close(ops.so3_rfft(x.to(dev), False, b_out), ref_f, "rfft" + tag)
             assert_close(ops.so3_rifft(s.to(dev), False, b_out), ref_i, "rifft" + tag)
             assert_close(ops.so3_fft(xc.to(dev), True, b_out), ref_c, "fft" + tag)
             assert_close(ops.so3_ifft(s.to(dev), True, b_out), ref_ic, "ifft" + tag)
     finally:
         ops.lib.s2c_debug_force_general_path(0)
-        ops.lib.s2c_debug_plane_width(0)
+        ops.lib.s2c_debug_plane_chunk(0)
