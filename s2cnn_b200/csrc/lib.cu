@@ -76,12 +76,12 @@ static int launch_inv_plane(int N, long zc, stream_t st, const InvPlaneParams& f
   return S2C_LAUNCH_PLANE(so3_inv_plane, 64, grid, st, f);
 }
 static int launch_fwd_rows(int N, stream_t st, const FwdRowsParams& f) {
-  if (N == 128) return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 128, rows_grid(f.K), st, f);
-  return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 64, rows_grid(f.K), st, f);
+  if (N == 128) return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 128, rows_grid(f.K, f.zc), st, f);
+  return S2C_LAUNCH_ROWS(so3_fwd_wigner_r, 64, rows_grid(f.K, f.zc), st, f);
 }
 static int launch_inv_rows(int N, stream_t st, const InvRowsParams& f) {
-  if (N == 128) return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 128, rows_grid(f.K), st, f);
-  return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 64, rows_grid(f.K), st, f);
+  if (N == 128) return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 128, rows_grid(f.K, f.zc), st, f);
+  return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 64, rows_grid(f.K, f.zc), st, f);
 }
 
 static int check_b(int b_in, int b_out) {

@@ -118,25 +118,38 @@ struct so3_fwd_plane_impl {
     const int K = p.K;
     const long z = ctx.bid / N;
     const int beta = (int)(ctx.bid - z * N);
+    // ---- FFT over gamma of the packed row pairs (t, t + N/2) -----------------------------------
+    // The loads of batch k + 1 are issued before batch k is transformed, so a global-memory
+    // latency is exposed once per plane instead of once per batch.
+    const long plane0 = ((z * N + beta) * N) * (long)N;
+    constexpr int IT = (RW * RB + 31) / 32;          // batches of 32 (row, j) items per row group
+    auto load_batch = [&](int bi, float2 (&v)[8]) {
+      const int g = (bi / IT) * NW + warp;
+      const int it = (bi % IT) * 32 + lane, tl = it / RB, j = it % RB;
+      if (RW * RB < 32 && it >= RW * RB) return;
+      const long e1 = plane0 + (long)plane_row(RW, g, tl) * N + j;
+      const long e2 = e1 + (long)(N / 2) * N;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[k].x = plane_ld_stream(p.x + (e1 + RB * k) * p.in_stride + p.in_off);
+        v[k].y = plane_ld_stream(p.x + (e2 + RB * k) * p.in_stride + p.in_off);
+      }
+    };
+    float2 vnext[8];
+    load_batch(0, vnext);
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
     ctx.sync();
-
-    // ---- FFT over gamma of the packed row pairs (t, t + N/2) -----------------------------------
-    const long plane0 = ((z * N + beta) * N) * (long)N;
+#pragma unroll
     for (int gi = 0; gi < NG; ++gi) {
       const int g = gi * NW + warp;
 #pragma unroll
-      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
-        const int it = it0 + lane, tl = it / RB, j = it % RB;
-        if (RW * RB < 32 && it >= RW * RB) continue;
-        const long e1 = plane0 + (long)plane_row(RW, g, tl) * N + j;
-        const long e2 = e1 + (long)(N / 2) * N;
+      for (int ii = 0; ii < IT; ++ii) {
+        const int it = ii * 32 + lane, tl = it / RB, j = it % RB;
         float2 v[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          v[k].x = plane_ld_stream(p.x + (e1 + RB * k) * p.in_stride + p.in_off);
-          v[k].y = plane_ld_stream(p.x + (e2 + RB * k) * p.in_stride + p.in_off);
-        }
+        for (int k = 0; k < 8; ++k) v[k] = vnext[k];
+        if (gi * IT + ii + 1 < NG * IT) load_batch(gi * IT + ii + 1, vnext);
+        if (RW * RB < 32 && it >= RW * RB) continue;
         fft_reg<8, -1>(v, tw);
         plane_put_step1<8, RB, -1>(v, wtmp + tl * LDT + j, j, tw);
       }
@@ -219,6 +232,29 @@ struct so3_inv_plane_impl {
     const int K = p.K;
     const long z = ctx.bid / N;
     const int beta = (int)(ctx.bid - z * N);
+    // ---- inverse FFT over m -> alpha of the kept columns, packed into row pairs on store --------
+    // The rows of batch k + 1 are requested before batch k is transformed (see so3_fwd_plane).
+    const int nchunks = (K + 31) / 32;
+    constexpr int IT = (RW * RB + 31) / 32;
+    auto load_batch = [&](int bi, float2 (&v)[8]) {
+      const int c = bi / IT;
+      const int n0 = c * 32 + plane_col0(RW, warp);   // this warp's columns: n0 + 8 i, i < RW
+      const int it = (bi % IT) * 32 + lane, i = it / RB, j = it % RB;
+      const int n = (RW * RB < 32 && it >= RW * RB) ? K : n0 + 8 * i;
+      if (n < K) {
+        // bins j + RB k of the row of this (n, z, beta): RB neighbouring lanes read RB * 8
+        // contiguous bytes per k
+        const float2* srow = p.s + (((long)n * p.nbatch + z) * N + beta) * N + j;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int f = j + RB * k;
+          const int m = f < N / 2 ? f : f - N;
+          v[k] = (m > -K && m < K) ? srow[RB * k] : make_float2(0.f, 0.f);
+        }
+      }
+    };
+    float2 vnext[8];
+    load_batch(0, vnext);
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
     {  // frequencies K .. N-K of every packed row are zero
       const int cnt = N - 2 * K + 1;
@@ -228,26 +264,17 @@ struct so3_inv_plane_impl {
       }
     }
     ctx.sync();
-
-    // ---- inverse FFT over m -> alpha of the kept columns, packed into row pairs on store --------
-    const int nchunks = (K + 31) / 32;
     for (int c = 0; c < nchunks; ++c) {
-      const int n0 = c * 32 + plane_col0(RW, warp);   // this warp's columns: n0 + 8 i, i < RW
+      const int n0 = c * 32 + plane_col0(RW, warp);
 #pragma unroll
-      for (int it0 = 0; it0 < RW * RB; it0 += 32) {
-        const int it = it0 + lane, i = it / RB, j = it % RB;
+      for (int ii = 0; ii < IT; ++ii) {
+        const int it = ii * 32 + lane, i = it / RB, j = it % RB;
         const int n = (RW * RB < 32 && it >= RW * RB) ? K : n0 + 8 * i;
-        if (n < K) {
-          // bins j + RB k of the row of this (n, z, beta): RB neighbouring lanes read RB * 8
-          // contiguous bytes per k
-          const float2* srow = p.s + (((long)n * p.nbatch + z) * N + beta) * N + j;
-          float2 v[8];
+        float2 v[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int f = j + RB * k;
-            const int m = f < N / 2 ? f : f - N;
-            v[k] = (m > -K && m < K) ? srow[RB * k] : make_float2(0.f, 0.f);
-          }
+        for (int k = 0; k < 8; ++k) v[k] = vnext[k];
+        if (c * IT + ii + 1 < nchunks * IT) load_batch(c * IT + ii + 1, vnext);
+        if (n < K) {
           fft_reg<8, +1>(v, tw);
           plane_put_step1<8, RB, +1>(v, wtmp + i * LDA + j, j, tw);
         }

@@ -7,22 +7,26 @@
 // of the reference's so3fft.cu / so3ifft.cu tile loops (s2cnn/soft/so3_fft.py:296-336, :391-431).
 //
 // Organisation: the 32 lanes of a warp split the BETA axis; a warp owns the frequency pair
-// (+m, n) and (-m, n) for four batch elements, a block of 8 warps four values of |m| times two
-// groups of four batch elements.
+// (+m, n) and (-m, n) for four batch elements, a block of 8 warps eight consecutive values of |m|.
 //   * The table holds only the first half of the beta range (TableCache::half_panels): the
 //     SOFT grid maps onto itself under beta -> pi - beta and
 //         d^l_{m,n}(pi - beta_j) = (-1)^(l+n) d^l_{-m,n}(beta_j),
 //     so the second half of panel (m, n) is the first half of panel (-m, n) up to that sign.  A warp
-//     reads row l of both half panels once - 2 x N/2 consecutive floats, one coalesced load per
-//     lane - and uses each for both members of its pair.
+//     reads row l of both half panels once and uses each for both members of its pair.
+//   * Panel rows reach a warp through a private ring in shared memory filled by 16-byte
+//     asynchronous copies (cp.async), kRowsDepth - 1 steps ahead of their use: with one outstanding
+//     row per warp the kernels ran at the latency, not the bandwidth, of L2 / HBM.  (Copies of 4 or
+//     8 bytes per lane cost about six times the shared-memory wavefronts of 16-byte ones, so a lane
+//     copies 16 bytes and reads the 4 or 8 bytes it needs after a warp barrier.)
 //   * analysis: the warp keeps its slice of V in registers for the whole pair and streams the
-//     panel rows; every degree ends with a sum over the lanes (a 32-value transpose-reduce by
-//     shuffles for two degrees at a time, after which lane i holds value i).
+//     panel rows; every two degrees end with a sum over the lanes (a 32-value transpose-reduce by
+//     shuffles, after which lane i holds value i).
 //   * synthesis: the accumulators (one beta slice of four signals per lane) stay in registers
 //     while the rows stream; no cross-lane traffic at all.
-//   * V is [n][z][beta][f] (f = alpha-frequency bin, see so3_plane_kernels.h): the block moves its
-//     8 columns (+-m) between global and shared memory one 32-byte sector per (z, beta) at a time and
-//     the lanes read / write the transposed tile [column][z][beta] without bank conflicts.
+//   * V is [n][z][beta][f] (f = alpha-frequency bin, see so3_plane_kernels.h): rows of one (z, beta)
+//     are 8 N bytes apart, so the block moves its 16 columns (+-m) between global and shared memory
+//     as 64-byte runs - four neighbouring lanes, 16 bytes each, per run - and the lanes read / write
+//     the transposed tile [column][z][beta] without bank conflicts.
 #pragma once
 
 #include "backend.h"
@@ -30,10 +34,11 @@
 
 namespace s2c {
 
-constexpr int kRowsMG = 4;      // values of |m| per block
-constexpr int kRowsZH = 4;      // batch elements per warp
-constexpr int kRowsZC = 8;      // batch elements per block = chunk size the host uses
-constexpr int kRowsThreads = 32 * kRowsMG * (kRowsZC / kRowsZH);
+constexpr int kRowsMG = 8;      // values of |m| per block = warps per block
+constexpr int kRowsZQ = 4;      // batch elements per block (and per warp)
+constexpr int kRowsZC = 8;      // batch elements per chunk (what the host sizes V for)
+constexpr int kRowsThreads = 32 * kRowsMG;
+constexpr int kRowsDepth = 8;   // ring slots per warp
 
 struct HalfPanelsDev {
   int nbeta;                // N = 2 b of the beta grid
@@ -58,41 +63,34 @@ struct InvRowsParams {
   int zc, K, mode;      // mode: kSo3Real or kSo3RotI
 };
 
-// Panel rows reach a warp through a private ring of kRowsDepth steps in shared memory, filled by
-// asynchronous copies (cp.async): every lane copies and later reads only its own beta slice, so
-// the ring needs no barrier, only the per-thread wait for the oldest copy group - and the rows of
-// the next kRowsDepth steps are in flight while the current one is being used (with one
-// outstanding row per warp the kernels ran at the latency, not the bandwidth, of L2 / HBM).
-constexpr int kRowsDepth = 8;
-
-// shared memory: the tile [8 columns][zc = 8][N beta] of complex numbers.  The rings [warp][depth]
-// [rows per step][A, B][N / 2] live inside it: the analysis is done with the tile once every warp
-// has its slice of V in registers (whole tile = 8 rings of depth 8 x 2 rows), the synthesis keeps
-// the symmetrised spectrum rows in the lower half until the tile is written and its rings (depth 8
-// x 1 row) in the upper half.  (+ in the host-emulation build a per-warp exchange buffer that
-// stands in for the shuffles.)
+// Shared memory: the tile [16 columns][4 z][N beta] of complex numbers with a column stride of
+// 4 N + 2 (so that four lanes storing to four columns hit four different bank groups).  The rings
+// [warp][depth][rows per step][A, B][N / 2] live inside it: the analysis is done with the tile once
+// every warp has its slice of V in registers (8 rings of depth 8 x 2 rows fill it), the synthesis
+// keeps the symmetrised spectrum rows in the lower half until the tile is written and its rings
+// (depth 8 x 1 row) in the upper half.  (+ in the host-emulation build a per-warp exchange buffer
+// that stands in for the shuffles.)
 template <int N>
-S2C_HD constexpr int rows_tile_floats() { return 2 * kRowsMG * kRowsZC * N * 2; }
+S2C_HD constexpr int rows_cs() { return kRowsZQ * N + 2; }
+template <int N>
+S2C_HD constexpr int rows_tile_floats() { return 2 * kRowsMG * rows_cs<N>() * 2; }
 template <int N>
 S2C_HD constexpr int rows_ring_floats(int rows_per_step) { return kRowsDepth * rows_per_step * 2 * (N / 2); }
 template <int N>
 inline size_t rows_smem_bytes() {
-  static_assert((kRowsThreads / 32) * rows_ring_floats<N>(2) <= rows_tile_floats<N>(), "analysis rings");
-  static_assert((kRowsThreads / 32) * rows_ring_floats<N>(1) <= rows_tile_floats<N>() / 2, "synthesis rings");
+  static_assert(kRowsMG * rows_ring_floats<N>(2) <= rows_tile_floats<N>(), "analysis rings");
+  static_assert(kRowsMG * rows_ring_floats<N>(1) <= rows_tile_floats<N>() / 2, "synthesis rings");
   size_t b = (size_t)rows_tile_floats<N>() * sizeof(float);
 #ifdef S2C_EMUL
-  b += (size_t)(kRowsThreads / 32) * 32 * 33 * sizeof(float);
+  b += (size_t)kRowsMG * 32 * 33 * sizeof(float);
 #endif
   return b;
 }
 
-// JL consecutive floats global -> shared, asynchronously; groups complete in issue order
+// 16 bytes global -> shared, asynchronously; groups complete in issue order
 #ifndef S2C_EMUL
-template <int JL>
-S2C_D void rows_copy_async(float* dst, const float* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(dst)), "l"(src),
-               "n"(JL * 4)
-               : "memory");
+S2C_D void rows_copy16_async(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 S2C_D void rows_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // kRowsDepth - 1 steps are in flight: wait until at most kRowsDepth - 2 of this thread's copy
@@ -102,9 +100,8 @@ S2C_D void rows_wait_oldest() {
   asm volatile("cp.async.wait_group %0;" ::"n"(kRowsDepth - 2) : "memory");
 }
 #else
-template <int JL>
-inline void rows_copy_async(float* dst, const float* src) {
-  for (int i = 0; i < JL; ++i) dst[i] = src[i];
+inline void rows_copy16_async(float* dst, const float* src) {
+  for (int i = 0; i < 4; ++i) dst[i] = src[i];
 }
 inline void rows_commit() {}
 inline void rows_wait_oldest() {}
@@ -147,20 +144,24 @@ inline float rows_partner(const Ctx& ctx, float v, int lane, float* xch) {
 }
 #endif
 
-// which (n, |m| group) a block owns, and the columns of its tile:
-//   c < kRowsMG:  frequency +(m0 + c)  at bin f = m0 + c
-//   c >= kRowsMG: frequency -(m0 + c - kRowsMG) at bin f = N - (m0 + c - kRowsMG)   (not for m = 0)
+// which (n, |m| group, z quad) a block owns, and the columns of its tile:
+//   c < 8:   frequency +(m0 + c)      at bin f = m0 + c
+//   c >= 8:  frequency -(m0 + c - 8)  at bin f = N - (m0 + c - 8)      (not for m = 0)
 struct RowsGeom {
-  int n, m0;
+  int n, m0, zq;
 };
-S2C_D RowsGeom rows_geom(int bid, int K) {
-  const int ngroups = (K + kRowsMG - 1) / kRowsMG;
+S2C_D RowsGeom rows_geom(int bid, int K, int zc) {
+  const int ngroups = (K + kRowsMG - 1) / kRowsMG, nzq = (zc + kRowsZQ - 1) / kRowsZQ;
   RowsGeom g;
-  g.n = bid / ngroups;
-  g.m0 = (bid - g.n * ngroups) * kRowsMG;
+  g.zq = bid % nzq;
+  const int t = bid / nzq;
+  g.n = t / ngroups;
+  g.m0 = (t - g.n * ngroups) * kRowsMG;
   return g;
 }
-inline long rows_grid(int K) { return (long)K * ((K + kRowsMG - 1) / kRowsMG); }
+inline long rows_grid(int K, int zc) {
+  return (long)K * ((K + kRowsMG - 1) / kRowsMG) * ((zc + kRowsZQ - 1) / kRowsZQ);
+}
 
 // half-panel rows of the pair (+m, n) and (-m, n); for n = 0 only m >= 0 is stored and
 // d_{-m,0} = (-1)^m d_{m,0}; for m = 0 the two coincide
@@ -182,6 +183,29 @@ S2C_D RowsPanels rows_panels(const HalfPanelsDev& pan, int m, int n) {
   return r;
 }
 
+// One ring step = S rows of both half panels: [row][A, B][NH] floats, copied 16 bytes per lane.
+template <int N, int S>
+S2C_D void rows_issue(float* ring, int t, const float* pa, const float* pb, int L, int lane) {
+  constexpr int NH = N / 2, P = NH / 4;      // 16-byte pieces per half-panel row
+  float* slot = ring + (t % kRowsDepth) * (S * 2 * NH);
+#pragma unroll
+  for (int piece = lane; piece < S * 2 * P; piece += 32) {
+    const int r = piece / (2 * P), rem = piece - r * 2 * P, ab = rem / P, q = rem - ab * P;
+    const int row = S * t + r;
+    if (row < L)
+      rows_copy16_async(slot + (r * 2 + ab) * NH + 4 * q, (ab ? pb : pa) + (long)row * NH + 4 * q);
+  }
+  rows_commit();   // one group per step, empty or not, so that the wait counts steps
+}
+
+// The tile rows a thread moves: thread = (run piece q < 4, row r0 < 64), rows r0 + 64 k.
+template <int N>
+struct RowsTileMap {
+  static constexpr int kPasses = kRowsZQ * N / 64;
+  int q, r0;
+  S2C_D explicit RowsTileMap(int tid) : q(tid & 3), r0(tid >> 2) {}
+};
+
 // ---------------------------------------------------------------------------------------------
 // analysis:  X[l, +-m, n][z] = sum_beta W[l][beta] V[z][beta]   (+ Hermitian mirror rows)
 // ---------------------------------------------------------------------------------------------
@@ -189,57 +213,53 @@ template <int N>
 struct so3_fwd_wigner_r_impl {
   static S2C_D void run(const Ctx& ctx, const FwdRowsParams& p, unsigned char* smem) {
     constexpr int NH = N / 2, JL = NH / 32;           // betas of the half range per lane
-    constexpr int ZS = N, CS = kRowsZC * N;           // tile strides (complex): z, column
-    float2* tile = reinterpret_cast<float2*>(smem);   // [2 MG][ZC][N]
+    constexpr int ZS = N, CS = rows_cs<N>();          // tile strides (complex): z, column
+    float2* tile = reinterpret_cast<float2*>(smem);   // [16][4][N] (column stride CS)
     const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
     // ring step = two degrees: [depth][row 0 / 1][A / B][NH]; reuses the tile's memory (see below)
     float* ring = reinterpret_cast<float*>(smem) + warp * rows_ring_floats<N>(2);
     float* xch = reinterpret_cast<float*>(smem) + rows_tile_floats<N>() + warp * 32 * 33;
-    const RowsGeom g = rows_geom(ctx.bid, p.K);
-    const int n = g.n, m0 = g.m0, K = p.K, zc = p.zc;
+    const int K = p.K, zc = p.zc;
+    const RowsGeom g = rows_geom(ctx.bid, K, zc);
+    const int n = g.n, m0 = g.m0, zbase = g.zq * kRowsZQ;
 
     // ---- stage the block's columns of V: tile[c][z][beta] ----------------------------------------
-    // (z, beta) rows are 8 N bytes apart in V, so every load is a sector of its own; all loads of a
-    // thread are issued before the first value is used
+    // Per (z, beta) row: bins m0 .. m0+7 (64 aligned bytes) and bins N-m0-7 .. N-m0, read as the
+    // aligned run N-m0-8 .. N-m0-1 plus the single bin N-m0.  All loads of a thread are issued
+    // before the first value is used.
     {
-      constexpr int kIt = kRowsZC * N / kRowsThreads;   // rows per thread
-      static_assert(kRowsZC * N % kRowsThreads == 0, "tile rows per thread");
-      const float2* vn = p.v + (long)n * zc * N * N;
-      float4 p0[kIt], p1[kIt];
-      float2 ng[kIt][kRowsMG];
+      const RowsTileMap<N> tm(ctx.tid);
+      constexpr int kP = RowsTileMap<N>::kPasses;
+      const float2* vn = p.v + ((long)n * zc + zbase) * N * N;
+      float4 pos[kP], neg[kP];
+      float2 one[kP];
 #pragma unroll
-      for (int k = 0; k < kIt; ++k) {
-        const int it = ctx.tid + k * kRowsThreads;
-        const int z = it / N, beta = it - z * N;
-        p0[k] = p1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int c = 0; c < kRowsMG; ++c) ng[k][c] = make_float2(0.f, 0.f);
-        if (z < zc) {
-          const float2* row = vn + ((long)z * N + beta) * N;
-          p0[k] = *reinterpret_cast<const float4*>(row + m0);
-          p1[k] = *reinterpret_cast<const float4*>(row + m0 + 2);
-#pragma unroll
-          for (int c = 0; c < kRowsMG; ++c)
-            if (m0 + c > 0) ng[k][c] = row[N - m0 - c];
+      for (int k = 0; k < kP; ++k) {
+        const int r = tm.r0 + 64 * k, z = r / N;
+        pos[k] = neg[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        one[k] = make_float2(0.f, 0.f);
+        if (zbase + z < zc) {
+          const float2* row = vn + (long)r * N;           // r = z * N + beta
+          pos[k] = *reinterpret_cast<const float4*>(row + m0 + 2 * tm.q);
+          neg[k] = *reinterpret_cast<const float4*>(row + N - m0 - 8 + 2 * tm.q);
+          if (tm.q == 0 && m0 > 0) one[k] = row[N - m0];
         }
       }
 #pragma unroll
-      for (int k = 0; k < kIt; ++k) {
-        const int it = ctx.tid + k * kRowsThreads;
-        const int z = it / N, beta = it - z * N;
+      for (int k = 0; k < kP; ++k) {
+        const int r = tm.r0 + 64 * k, z = r / N, beta = r - z * N;
         float2* dst = tile + z * ZS + beta;
-        dst[0 * CS] = make_float2(p0[k].x, p0[k].y);
-        dst[1 * CS] = make_float2(p0[k].z, p0[k].w);
-        dst[2 * CS] = make_float2(p1[k].x, p1[k].y);
-        dst[3 * CS] = make_float2(p1[k].z, p1[k].w);
-#pragma unroll
-        for (int c = 0; c < kRowsMG; ++c) dst[(kRowsMG + c) * CS] = ng[k][c];
+        dst[(2 * tm.q) * CS] = make_float2(pos[k].x, pos[k].y);
+        dst[(2 * tm.q + 1) * CS] = make_float2(pos[k].z, pos[k].w);
+        // bins N-m0-8+2q, N-m0-7+2q are the frequencies -(m0+8-2q), -(m0+7-2q)
+        if (tm.q > 0) dst[(16 - 2 * tm.q) * CS] = make_float2(neg[k].x, neg[k].y);
+        dst[(15 - 2 * tm.q) * CS] = make_float2(neg[k].z, neg[k].w);
+        if (tm.q == 0) dst[8 * CS] = one[k];
       }
     }
     ctx.sync();
 
-    const int mi = warp % kRowsMG, zh = warp / kRowsMG;
-    const int m = m0 + mi;
+    const int m = m0 + warp;
     const int lmin = m > n ? m : n;
     const int L = (m < K) ? p.nl - lmin : 0;
 #ifdef S2C_EMUL
@@ -250,15 +270,15 @@ struct so3_fwd_wigner_r_impl {
 #endif
 
     // ---- this lane's slice of V: betas j (p) and N-1-j (q) of the columns +m and -m ----------------
-    float2 vp[2][kRowsZH][JL], vq[2][kRowsZH][JL];
+    float2 vp[2][kRowsZQ][JL], vq[2][kRowsZQ][JL];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
-      for (int z = 0; z < kRowsZH; ++z)
+      for (int z = 0; z < kRowsZQ; ++z)
 #pragma unroll
         for (int jj = 0; jj < JL; ++jj) {
           const int j = JL * lane + jj;
-          const float2* col = tile + (s * kRowsMG + mi) * CS + (zh * kRowsZH + z) * ZS;
+          const float2* col = tile + (s * kRowsMG + warp) * CS + z * ZS;
           vp[s][z][jj] = col[j];
           vq[s][z][jj] = col[N - 1 - j];
         }
@@ -268,30 +288,16 @@ struct so3_fwd_wigner_r_impl {
     pn.bsign = 1.f;
     if (L > 0) pn = rows_panels(p.pan, m, n);
     const bool self = (m == 0);
-    const float* pa = pn.a + JL * lane;
-    const float* pb = pn.b + JL * lane;
     ctx.sync();   // every warp has its slice of V in registers: the tile's memory becomes the rings
-
-    // step t of the ring holds rows 2t and 2t + 1 (this lane's JL betas of each)
-    auto issue = [&](int t) {
-      float* slot = ring + (t % kRowsDepth) * (4 * NH) + JL * lane;
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-        if (2 * t + r < L) {
-          rows_copy_async<JL>(slot + (2 * r) * NH, pa + (long)(2 * t + r) * NH);
-          rows_copy_async<JL>(slot + (2 * r + 1) * NH, pb + (long)(2 * t + r) * NH);
-        }
-      rows_commit();   // one group per step, empty or not, so that the wait below counts steps
-    };
 #ifndef S2C_EMUL
     if (L <= 0) return;   // no block barrier below this point
 #endif
-    for (int t = 0; t < kRowsDepth - 1; ++t) issue(t);
+    for (int t = 0; t < kRowsDepth - 1; ++t) rows_issue<N, 2>(ring, t, pn.a, pn.b, L, lane);
 
     float va[2][JL], vb[2][JL];     // rows li, li + 1 of the two half panels
-    const int z0h = zh * kRowsZH;
     for (int li = 0; li < Lloop; li += 2) {
       rows_wait_oldest();
+      ctx.sync_warp();              // the other lanes' pieces of this step have landed, too
       {
         const float* slot = ring + ((li / 2) % kRowsDepth) * (4 * NH) + JL * lane;
 #pragma unroll
@@ -303,14 +309,14 @@ struct so3_fwd_wigner_r_impl {
             vb[r][jj] = ok ? pn.bsign * slot[(2 * r + 1) * NH + jj] : 0.f;
           }
       }
-      issue(li / 2 + kRowsDepth - 1);
+      rows_issue<N, 2>(ring, li / 2 + kRowsDepth - 1, pn.a, pn.b, L, lane);
       float val[32];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int l = lmin + li + r;
         const float sl = ((l + n) & 1) ? -1.f : 1.f;
 #pragma unroll
-        for (int z = 0; z < kRowsZH; ++z) {
+        for (int z = 0; z < kRowsZQ; ++z) {
           float pr = 0.f, pi = 0.f, qr = 0.f, qi = 0.f;
 #pragma unroll
           for (int jj = 0; jj < JL; ++jj) {
@@ -331,7 +337,7 @@ struct so3_fwd_wigner_r_impl {
       const float other = rows_partner(ctx, mine, lane, xch);  // the other component of the number
       // lane = r * 16 + s * 8 + z * 2 + c
       const int r = lane >> 4, s = (lane >> 3) & 1, z = (lane >> 1) & 3, c = lane & 1;
-      const int l = lmin + li + r, zz = z0h + z;
+      const int l = lmin + li + r, zz = zbase + z;
       if (li + r < L && zz < zc && !(self && s == 1)) {
         const int mm = s ? -m : m;
         float* o1 = reinterpret_cast<float*>(p.out + so3_row(l, mm, n) * p.out_zstride + zz) + c;
@@ -357,34 +363,34 @@ template <int N>
 struct so3_inv_wigner_r_impl {
   static S2C_D void run(const Ctx& ctx, const InvRowsParams& p, unsigned char* smem) {
     constexpr int NH = N / 2, JL = NH / 32;
-    constexpr int ZS = N, CS = kRowsZC * N;
-    float2* tile = reinterpret_cast<float2*>(smem);     // [2 MG][ZC][N], written after the loop
-    float2* xs = tile;                                    // before: [2 MG][Lmax][ZC] symmetrised rows
+    constexpr int ZS = N, CS = rows_cs<N>();
+    float2* tile = reinterpret_cast<float2*>(smem);     // [16][4][N], written after the loop
+    float2* xs = tile;                                    // before: [16][Lmax][4] symmetrised rows
     const int warp = ctx.tid >> 5, lane = ctx.tid & 31;
     // ring step = one degree: [depth][A / B][NH], in the upper half of the tile's memory
     float* ring = reinterpret_cast<float*>(smem) + rows_tile_floats<N>() / 2 + warp * rows_ring_floats<N>(1);
-    const RowsGeom g = rows_geom(ctx.bid, p.K);
-    const int n = g.n, m0 = g.m0, K = p.K, zc = p.zc, nl = p.pan.nl;
+    const int K = p.K, zc = p.zc, nl = p.pan.nl;
+    const RowsGeom g = rows_geom(ctx.bid, K, zc);
+    const int n = g.n, m0 = g.m0, zbase = g.zq * kRowsZQ;
     const int lmin_blk = m0 > n ? m0 : n;
     const int Lmax = nl - lmin_blk;                      // rows of the block's longest pair (<= N/2)
 
-    // ---- symmetrised spectrum rows of the block's 8 columns: xs[c][li][z], li from lmin_blk -------
-    // thread = (z, li mod 32); the loads of all 8 columns are issued before any is used
+    // ---- symmetrised spectrum rows of the block's 16 columns: xs[c][li][z], li from lmin_blk ------
+    // thread = (z, li); the loads of all 16 columns are issued before any is used
     {
-      const int z = ctx.tid % kRowsZC;
-      for (int li = ctx.tid / kRowsZC; li < Lmax; li += kRowsThreads / kRowsZC) {
+      const int z = ctx.tid % kRowsZQ;
+      for (int li = ctx.tid / kRowsZQ; li < Lmax; li += kRowsThreads / kRowsZQ) {
         const int l = lmin_blk + li;
         float2 a[2 * kRowsMG], b[2 * kRowsMG];
-        bool ok[2 * kRowsMG];
 #pragma unroll
         for (int c = 0; c < 2 * kRowsMG; ++c) {
           const int mabs = m0 + (c % kRowsMG);
           const int mm = c < kRowsMG ? mabs : -mabs;
-          ok[c] = z < zc && mabs < K && l >= mabs && !(c >= kRowsMG && mabs == 0);
+          const bool ok = zbase + z < zc && mabs < K && l >= mabs && !(c >= kRowsMG && mabs == 0);
           a[c] = b[c] = make_float2(0.f, 0.f);
-          if (ok[c]) {
-            a[c] = p.x[so3_row(l, mm, n) * p.x_zstride + z];
-            b[c] = p.x[so3_row(l, -mm, -n) * p.x_zstride + z];
+          if (ok) {
+            a[c] = p.x[so3_row(l, mm, n) * p.x_zstride + zbase + z];
+            b[c] = p.x[so3_row(l, -mm, -n) * p.x_zstride + zbase + z];
           }
         }
 #pragma unroll
@@ -397,57 +403,61 @@ struct so3_inv_wigner_r_impl {
             w = make_float2(w.y, -w.x);
           }
           const float fudge = ((mm - n) & 1) ? -1.f : 1.f;
-          xs[(c * Lmax + li) * kRowsZC + z] =
+          xs[(c * Lmax + li) * kRowsZQ + z] =
               make_float2(0.5f * (u.x + fudge * w.x), 0.5f * (u.y - fudge * w.y));
         }
       }
     }
     ctx.sync();
 
-    const int mi = warp % kRowsMG, zh = warp / kRowsMG;
-    const int m = m0 + mi;
+    const int m = m0 + warp;
     const int lmin = m > n ? m : n;
     const int L = (m < K) ? nl - lmin : 0;
-    const bool self = (m == 0);
+#ifdef S2C_EMUL
+    const int Lloop = Lmax;        // uniform over the block: a warp barrier is a block barrier here
+#else
+    const int Lloop = L;
+#endif
 
     // accumulators: betas j (p) and N-1-j (q) of the columns +m (0) and -m (1)
-    float2 sp[2][kRowsZH][JL], sq[2][kRowsZH][JL];
+    float2 sp[2][kRowsZQ][JL], sq[2][kRowsZQ][JL];
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
-      for (int z = 0; z < kRowsZH; ++z)
+      for (int z = 0; z < kRowsZQ; ++z)
 #pragma unroll
         for (int jj = 0; jj < JL; ++jj) sp[s][z][jj] = sq[s][z][jj] = make_float2(0.f, 0.f);
 
-    if (L > 0) {
-      const RowsPanels pn = rows_panels(p.pan, m, n);
-      const float* pa = pn.a + JL * lane;
-      const float* pb = pn.b + JL * lane;
-      const float2* x0 = xs + ((0 * kRowsMG + mi) * Lmax + (lmin - lmin_blk)) * kRowsZC + zh * kRowsZH;
-      const float2* x1 = xs + ((1 * kRowsMG + mi) * Lmax + (lmin - lmin_blk)) * kRowsZC + zh * kRowsZH;
-      auto issue = [&](int t) {
-        float* slot = ring + (t % kRowsDepth) * (2 * NH) + JL * lane;
-        if (t < L) {
-          rows_copy_async<JL>(slot, pa + (long)t * NH);
-          rows_copy_async<JL>(slot + NH, pb + (long)t * NH);
-        }
-        rows_commit();
-      };
-      for (int t = 0; t < kRowsDepth - 1; ++t) issue(t);
+    {
+      RowsPanels pn;
+      pn.a = pn.b = p.pan.data;
+      pn.bsign = 1.f;
+      if (L > 0) pn = rows_panels(p.pan, m, n);
+      const int lrel = L > 0 ? lmin - lmin_blk : 0;
+      const float2* x0 = xs + ((0 * kRowsMG + warp) * Lmax + lrel) * kRowsZQ;
+      const float2* x1 = xs + ((1 * kRowsMG + warp) * Lmax + lrel) * kRowsZQ;
+      if (Lloop > 0)
+        for (int t = 0; t < kRowsDepth - 1; ++t) rows_issue<N, 1>(ring, t, pn.a, pn.b, L, lane);
       float a[JL], b[JL];
-      for (int li = 0; li < L; ++li) {
+      for (int li = 0; li < Lloop; ++li) {
         rows_wait_oldest();
+        ctx.sync_warp();            // the other lanes' pieces of this row have landed, too
+        const bool act = li < L;
         {
           const float* slot = ring + (li % kRowsDepth) * (2 * NH) + JL * lane;
 #pragma unroll
-          for (int jj = 0; jj < JL; ++jj) { a[jj] = slot[jj]; b[jj] = pn.bsign * slot[NH + jj]; }
+          for (int jj = 0; jj < JL; ++jj) {
+            a[jj] = act ? slot[jj] : 0.f;
+            b[jj] = act ? pn.bsign * slot[NH + jj] : 0.f;
+          }
         }
-        issue(li + kRowsDepth - 1);
+        rows_issue<N, 1>(ring, li + kRowsDepth - 1, pn.a, pn.b, L, lane);
+        if (!act) continue;
         const int l = lmin + li;
         const float sl = ((l + n) & 1) ? -1.f : 1.f;
 #pragma unroll
-        for (int z = 0; z < kRowsZH; ++z) {
-          const float2 xp = x0[li * kRowsZC + z], xm = x1[li * kRowsZC + z];
+        for (int z = 0; z < kRowsZQ; ++z) {
+          const float2 xp = x0[li * kRowsZQ + z], xm = x1[li * kRowsZQ + z];
 #pragma unroll
           for (int jj = 0; jj < JL; ++jj) {
             const float sa = sl * a[jj], sb = sl * b[jj];
@@ -460,46 +470,47 @@ struct so3_inv_wigner_r_impl {
         }
       }
     }
-    ctx.sync();   // every warp is done with the spectrum rows; the same memory becomes the tile
+    ctx.sync();   // every warp is done with the spectrum rows and its ring; the memory becomes the tile
 
 #pragma unroll
     for (int s = 0; s < 2; ++s)
 #pragma unroll
-      for (int z = 0; z < kRowsZH; ++z)
+      for (int z = 0; z < kRowsZQ; ++z)
 #pragma unroll
         for (int jj = 0; jj < JL; ++jj) {
           const int j = JL * lane + jj;
-          float2* col = tile + (s * kRowsMG + mi) * CS + (zh * kRowsZH + z) * ZS;
+          float2* col = tile + (s * kRowsMG + warp) * CS + z * ZS;
           col[j] = sp[s][z][jj];
           col[N - 1 - j] = sq[s][z][jj];
         }
     ctx.sync();
 
-    // ---- tile -> V[n][z][beta][f]: bins m0 .. m0+3 as one sector, bins N - m singly -----------------
+    // ---- tile -> V[n][z][beta][f], the transfer of the analysis reversed ----------------------------
+    // Only bins of this block's own frequencies are written: m0 .. m0+7 (all of them: bins of
+    // frequencies >= K are never read by anyone) and N - m for m0 <= m <= m0+7, 0 < m < K.
     {
-      float2* vn = p.s + (long)n * zc * N * N;
-      for (int it = ctx.tid; it < kRowsZC * N; it += ctx.nthr) {
-        const int z = it / N, beta = it - z * N;
-        if (z >= zc) continue;
-        const float2* src = tile + z * ZS + beta;
-        float2* row = vn + ((long)z * N + beta) * N;
-        const float2 c0 = src[0 * CS], c1 = src[1 * CS], c2 = src[2 * CS], c3 = src[3 * CS];
-        if (m0 + 3 < K) {
-          *reinterpret_cast<float4*>(row + m0) = make_float4(c0.x, c0.y, c1.x, c1.y);
-          *reinterpret_cast<float4*>(row + m0 + 2) = make_float4(c2.x, c2.y, c3.x, c3.y);
-        } else {
-          if (m0 < K) row[m0] = c0;
-          if (m0 + 1 < K) row[m0 + 1] = c1;
-          if (m0 + 2 < K) row[m0 + 2] = c2;
-        }
+      const RowsTileMap<N> tm(ctx.tid);
+      constexpr int kP = RowsTileMap<N>::kPasses;
+      float2* vn = p.s + ((long)n * zc + zbase) * N * N;
 #pragma unroll
-        for (int c = 0; c < kRowsMG; ++c) {
-          const int mm = m0 + c;
-          if (mm > 0 && mm < K) row[N - mm] = src[(kRowsMG + c) * CS];
+      for (int k = 0; k < kP; ++k) {
+        const int r = tm.r0 + 64 * k, z = r / N, beta = r - z * N;
+        if (zbase + z >= zc) continue;
+        const float2* src = tile + z * ZS + beta;
+        float2* row = vn + (long)r * N;
+        const float2 c0 = src[(2 * tm.q) * CS], c1 = src[(2 * tm.q + 1) * CS];
+        *reinterpret_cast<float4*>(row + m0 + 2 * tm.q) = make_float4(c0.x, c0.y, c1.x, c1.y);
+        const int m_hi = m0 + 8 - 2 * tm.q, m_lo = m0 + 7 - 2 * tm.q;   // bins N-m0-8+2q and the next
+        const float2 d_lo = src[(15 - 2 * tm.q) * CS];
+        if (tm.q > 0 && m_hi < K) {
+          const float2 d_hi = src[(16 - 2 * tm.q) * CS];
+          *reinterpret_cast<float4*>(row + N - m_hi) = make_float4(d_hi.x, d_hi.y, d_lo.x, d_lo.y);
+        } else if (m_lo < K) {
+          row[N - m_lo] = d_lo;
         }
+        if (tm.q == 0 && m0 > 0 && m0 < K) row[N - m0] = src[8 * CS];
       }
     }
-    (void)self;
   }
 };
 
