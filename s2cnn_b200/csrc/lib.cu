@@ -59,12 +59,6 @@ static size_t s2_ws_per_z(int N, int K) { return (size_t)(2 * K - 1) * N * sizeo
 // two kernels (b = 64: 8.4 MB per signal, 67 MB per chunk of the 126 MB).
 static size_t so3_v_per_z(int N, int K) { return (size_t)K * N * N * sizeof(float2); }
 static bool use_plane_kernels(int N) { return plane_supported(N) && g_force_general < 2; }
-static long plane_chunk(long nbatch, size_t ws_bytes, int N, int K) {
-  const int want = g_plane_chunk.load();
-  long chunk = (want >= 1 && want <= kRowsZC) ? want : kRowsZC;
-  chunk = std::min<long>(chunk, (long)(ws_bytes / so3_v_per_z(N, K)));
-  return std::min(chunk, nbatch);
-}
 static int launch_fwd_plane(int N, long zc, stream_t st, const FwdPlaneParams& f) {
   const long grid = zc * N;
   if (N == 128) return S2C_LAUNCH_PLANE(so3_fwd_plane, 128, grid, st, f);
@@ -82,6 +76,29 @@ static int launch_fwd_rows(int N, stream_t st, const FwdRowsParams& f) {
 static int launch_inv_rows(int N, stream_t st, const InvRowsParams& f) {
   if (N == 128) return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 128, rows_grid(f.K, f.zc), st, f);
   return S2C_LAUNCH_ROWS(so3_inv_wigner_r, 64, rows_grid(f.K, f.zc), st, f);
+}
+
+// Runs `first(z0, zc, buffer, stream)` then `second(z0, zc, buffer, stream)` for every chunk of the
+// batch, in order on the caller's stream, through one scratch buffer.  (Running the two kernel
+// kinds of neighbouring chunks concurrently on two streams through two half-size buffers was
+// measured slower: both kinds are limited by the same shared-memory / L1 data path.)
+template <class F1, class F2>
+static int plane_pipeline(long nbatch, int N, int K, void* ws, size_t ws_bytes, stream_t st,
+                          F1 first, F2 second) {
+  const size_t vz = so3_v_per_z(N, K);
+  const int want = g_plane_chunk.load();
+  const long fit = (long)(ws_bytes / vz);
+  if (fit < 1 || ws == nullptr)
+    return fail(S2C_ERR_WORKSPACE, "workspace smaller than one batch element (" + std::to_string(vz) +
+                                       " bytes needed)");
+  long chunk = (want >= 1 && want <= kRowsZC) ? want : kRowsZC;
+  chunk = std::min(std::min(chunk, fit), nbatch);
+  for (long z0 = 0; z0 < nbatch; z0 += chunk) {
+    const long zc = std::min(chunk, nbatch - z0);
+    S2C_TRY(first(z0, zc, (float2*)ws, st));
+    S2C_TRY(second(z0, zc, (float2*)ws, st));
+  }
+  return S2C_OK;
 }
 
 static int check_b(int b_in, int b_out) {
@@ -117,6 +134,25 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     return rc;
   }
   if (relu) return fail(S2C_ERR_UNSUPPORTED, "fused ReLU input needs the small-bandwidth path");
+  if (use_plane_kernels(N)) {
+    HalfPanelsDev hp;
+    hp.nbeta = N; hp.nl = b_out; hp.K = K; hp.npairs = pan.npairs;
+    S2C_TRY(TableCache::get().half_panels(b_in, b_out, K, weighted, &hp.data, &hp.off));
+    auto planes = [&](long z0, long zc, float2* v, stream_t s) {
+      FwdPlaneParams f;
+      f.x = x + (size_t)z0 * N * N * N * in_stride;
+      f.in_stride = in_stride; f.in_off = in_off;
+      f.v = v; f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
+      return launch_fwd_plane(N, zc, s, f);
+    };
+    auto wigner = [&](long z0, long zc, float2* v, stream_t s) {
+      FwdRowsParams r;
+      r.v = v; r.out = out + z0; r.out_zstride = nbatch; r.pan = hp;
+      r.zc = (int)zc; r.K = K; r.nl = b_out; r.mode = mode;
+      return launch_fwd_rows(N, s, r);
+    };
+    return plane_pipeline(nbatch, N, K, ws, ws_bytes, st, planes, wigner);
+  }
   const size_t per_z = so3_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || ws == nullptr)
@@ -124,29 +160,11 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
                                        std::to_string(per_z) + " bytes needed)");
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
-  const bool plane = use_plane_kernels(N);
-  HalfPanelsDev hp;
-  if (plane) {
-    chunk = plane_chunk(nbatch, ws_bytes, N, K);
-    hp.nbeta = N; hp.nl = b_out; hp.K = K; hp.npairs = pan.npairs;
-    S2C_TRY(TableCache::get().half_panels(b_in, b_out, K, weighted, &hp.data, &hp.off));
-  }
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     float2* u = (float2*)ws;
-    float2* v = plane ? u : u + (size_t)zc * K * N * N;
-    if (plane) {
-      FwdPlaneParams f;
-      f.x = x + (size_t)z0 * N * N * N * in_stride;
-      f.in_stride = in_stride; f.in_off = in_off;
-      f.v = v; f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
-      S2C_TRY(launch_fwd_plane(N, zc, st, f));
-      FwdRowsParams r;
-      r.v = v; r.out = out + z0; r.out_zstride = nbatch; r.pan = hp;
-      r.zc = (int)zc; r.K = K; r.nl = b_out; r.mode = mode;
-      S2C_TRY(launch_fwd_rows(N, st, r));
-      continue;
-    } else {
+    float2* v = u + (size_t)zc * K * N * N;
+    {
     FwdGammaParams g;
     g.x = x + (size_t)z0 * N * N * N * in_stride;
     g.in_stride = in_stride;
@@ -243,6 +261,27 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
   }
   if (integral)
     return fail(S2C_ERR_UNSUPPORTED, "fused ReLU + integration needs the small-bandwidth path");
+  if (use_plane_kernels(N)) {
+    HalfPanelsDev hp;
+    hp.nbeta = N; hp.nl = K; hp.K = K; hp.npairs = pan.npairs;
+    S2C_TRY(TableCache::get().half_panels(b_out, K, K, weighted, &hp.data, &hp.off));
+    auto wigner = [&](long z0, long zc, float2* s, stream_t sm) {
+      InvRowsParams r;
+      r.x = x + z0; r.x_zstride = nbatch; r.s = s; r.pan = hp;
+      r.zc = (int)zc; r.K = K; r.mode = mode;
+      return launch_inv_rows(N, sm, r);
+    };
+    auto planes = [&](long z0, long zc, float2* s, stream_t sm) {
+      InvPlaneParams f;
+      f.s = s;
+      f.out = out + (size_t)z0 * N * N * N * out_stride;
+      f.out_stride = out_stride; f.out_off = out_off;
+      f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1; f.z0 = z0;
+      f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
+      return launch_inv_plane(N, zc, sm, f);
+    };
+    return plane_pipeline(nbatch, N, K, ws, ws_bytes, st, wigner, planes);
+  }
   const size_t per_z = so3_ws_per_z(N, K);
   long chunk = (long)std::min<size_t>((size_t)nbatch, ws_bytes / per_z);
   if (chunk < 1 || ws == nullptr)
@@ -250,31 +289,10 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
                                        std::to_string(per_z) + " bytes needed)");
   const int G = fft_group(N, N), Gg = fft_group(N, N / 2);  // alpha passes, gamma passes
   const size_t fft_smem = fft_smem_bytes(N, G);
-  const bool plane = use_plane_kernels(N);
-  HalfPanelsDev hp;
-  if (plane) {
-    chunk = plane_chunk(nbatch, ws_bytes, N, K);
-    hp.nbeta = N; hp.nl = K; hp.K = K; hp.npairs = pan.npairs;
-    S2C_TRY(TableCache::get().half_panels(b_out, K, K, weighted, &hp.data, &hp.off));
-  }
   for (long z0 = 0; z0 < nbatch; z0 += chunk) {
     const long zc = std::min(chunk, nbatch - z0);
     float2* t = (float2*)ws;                                   // [z][K][N][N]
-    float2* s = plane ? t : t + (size_t)zc * K * N * N;        // [K][2K-1][z][N]
-    if (plane) {
-      InvRowsParams r;
-      r.x = x + z0; r.x_zstride = nbatch; r.s = s; r.pan = hp;
-      r.zc = (int)zc; r.K = K; r.mode = mode;
-      S2C_TRY(launch_inv_rows(N, st, r));
-      InvPlaneParams f;
-      f.s = s;
-      f.out = out + (size_t)z0 * N * N * N * out_stride;
-      f.out_stride = out_stride; f.out_off = out_off;
-      f.bias = bias; f.nfeat = nfeat > 0 ? nfeat : 1; f.z0 = z0;
-      f.tw = fft.tw; f.nbatch = (int)zc; f.K = K;
-      S2C_TRY(launch_inv_plane(N, zc, st, f));
-      continue;
-    }
+    float2* s = t + (size_t)zc * K * N * N;                    // [K][2K-1][z][N]
     InvWignerParams w;
     w.x = x + z0;
     w.x_zstride = nbatch;
