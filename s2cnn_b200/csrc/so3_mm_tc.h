@@ -21,13 +21,25 @@
 // kTcFlushBlocks K blocks the issuer switches to the other one, and while the tensor core fills
 // it the threads add the finished partial sum, rounding properly, into a third TMEM region.
 //
-// Tiling: one CTA per (l, 128-row tile, 128-column tile); the K loop walks the blocks (outer
-// contraction index, slice of its run of floats).  Operands are staged by all 512 threads into
-// shared memory in the canonical K-major, no-swizzle UMMA layout (8 rows x 16 bytes core matrices),
-// double buffered; one elected thread issues tcgen05.mma and commits to an mbarrier that releases
-// the stage.  The epilogue reads the accumulator with tcgen05.ld (32 lanes x 32 columns per warp
-// and instruction) and stores the result directly in its interleaved layout.  Every mbarrier wait
-// is bounded; on a time-out the kernel raises an error flag, frees its TMEM columns and returns.
+// Tiling: one CTA per (l, 128-row tile, 128-column tile); the K loop walks blocks of at most
+// kTcKMax floats (outer contraction index, slice of its run of floats).  The CTA is warp
+// specialised (17 warps):
+//   * 12 producer warps read the two operands from global memory (register prefetch one block
+//     ahead), split them into hi / lo TF32 parts and stage them in shared memory in the canonical
+//     K-major, no-swizzle UMMA layout (8 rows x 16 bytes core matrices), kTcStages stages deep; a
+//     warp arrives on the stage's "full" mbarrier once its lanes have written their share;
+//   * one issuer warp waits for "full", issues the nine tcgen05.mma of the block (hi*hi, lo*hi,
+//     hi*lo for each k-step of 8) from one elected lane and commits them to the stage's "empty"
+//     mbarrier, which lets the producers overwrite the stage; it alternates between two accumulators
+//     in tensor memory every kTcFlushBlocks blocks and commits to an "accumulator done" mbarrier;
+//   * 4 collector warps (one per TMEM lane quarter) add each finished accumulator, with proper
+//     rounding, into a third tensor-memory region and hand the accumulator back ("accumulator
+//     free") - all of it while the tensor core fills the other one.
+// The epilogue (all 16 non-issuer warps) reads the last accumulator and the sum region with
+// tcgen05.ld (32 lanes x 32 columns per warp and instruction) and stores the result directly in
+// its interleaved layout.  Every mbarrier wait is bounded; on a time-out the waiting thread raises a
+// block-wide abort flag, every role leaves its loop, the kernel raises the error flag, frees its
+// TMEM columns and returns.
 #pragma once
 
 #ifndef S2C_EMUL
@@ -77,17 +89,21 @@ __host__ __device__ __forceinline__ TcGeom tc_geom(int op, int nb, int fi, int f
 }
 
 constexpr int kTcBM = 128, kTcBN = 128;
-constexpr int kTcKMax = 48;                       // floats per K block
+constexpr int kTcKMax = 24;                       // floats per K block
+constexpr int kTcStages = 4;
 constexpr int kTcLBO = kTcBM * 16 + 16;           // bytes between K-adjacent core matrices (padded)
 constexpr int kTcSBO = 128;                       // bytes between row-adjacent core matrices
 constexpr int kTcBufBytes = (kTcKMax / 4) * kTcLBO;   // one operand buffer (hi or lo)
 constexpr int kTcStageBytes = 4 * kTcBufBytes;        // A hi, A lo, B hi, B lo
-constexpr int kTcSmemBytes = 2 * kTcStageBytes + 64;
-constexpr int kTcThreads = 512;
+constexpr int kTcSmemBytes = kTcStages * kTcStageBytes + 256;   // + mbarriers, TMEM slot, abort flag
+constexpr int kTcProducerWarps = 12, kTcCollectorWarps = 4;
+constexpr int kTcProducers = 32 * kTcProducerWarps;
+constexpr int kTcFirstProducer = 32 * (1 + kTcCollectorWarps);  // thread index of the first producer
+constexpr int kTcThreads = 32 * (1 + kTcCollectorWarps + kTcProducerWarps);
 // K blocks accumulated by the tensor core before the partial sum is added, in FP32 with rounding,
 // into the sum region (bounds the length of the tensor core's own accumulation chain, whose
-// additions truncate): 4 blocks = 72 MMAs per chain.
-constexpr int kTcFlushBlocks = 4;
+// additions truncate): 8 blocks = 72 MMAs per chain.
+constexpr int kTcFlushBlocks = 8;
 // tensor-memory columns: two alternating accumulators and the FP32 sum region (power of two)
 constexpr int kTcTmemCols = 512;
 constexpr int kTcSumCol = 2 * kTcBN;
@@ -206,17 +222,21 @@ __host__ __device__ __forceinline__ long tc_tiles_for(int op, int nb, int fi, in
   return ((M + kTcBM - 1) / kTcBM) * ((N + kTcBN - 1) / kTcBN);
 }
 
-// FLUSH = false drops the partial-sum code (fewer registers); valid while no degree needs more than
-// kTcFlushBlocks K blocks.
+// FLUSH = false drops the partial-sum code; valid while no CTA needs more than kTcFlushBlocks K
+// blocks.
 // VEC = true: 16-byte loads and stores (feature counts - for grad y the batch - even); VEC = false:
 // 8-byte accesses, any sizes.
 template <int OP, bool FLUSH, bool VEC>
 __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(s2c_dyn_smem);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + 2 * kTcStageBytes);      // [2] stages
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 2 * kTcStageBytes + 16);
-  uint64_t* flushbar = reinterpret_cast<uint64_t*>(smem + 2 * kTcStageBytes + 32);
+  unsigned char* ctl = smem + kTcStages * kTcStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ctl);                 // [stages] producers -> issuer
+  uint64_t* empty = full + kTcStages;                                // [stages] tensor core -> producers
+  uint64_t* accdone = empty + kTcStages;                             // [2] tensor core -> collectors
+  uint64_t* accfree = accdone + 2;                                   // [2] collectors -> issuer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfree + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---- which tile ---------------------------------------------------------------------------
@@ -241,19 +261,20 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   const int row0 = (int)(t / tiles_n) * kTcBM, col0 = (int)(t % tiles_n) * kTcBN;
   const long spec0 = (long)l * (4L * l * l - 1) / 3;
   const int fi2 = 2 * p.fi, fo2 = 2 * p.fo;
-  // operand addressing (floats): offset of outer contraction index `o`, element `kf` of its run =
-  //   contiguous:  o * ko + kf          strided:  o * ko + (kf / 2) * st + (kf % 2)
-  constexpr bool a_str = OP == kTcGradY, b_str = OP != kTcGradX;
-  long a_ko, b_ko, a_st = 0, b_st = 0;
-  if (OP == kTcFwd)        { a_ko = (long)p.nb * fi2;      b_ko = (long)p.fi * fo2;      b_st = fo2; }
-  else if (OP == kTcGradX) { a_ko = (long)p.nb * fo2;      b_ko = (long)L * p.fi * fo2; }
-  else                       { a_ko = (long)L * p.nb * fi2;  b_ko = (long)L * p.nb * fo2;  a_st = fi2; b_st = fo2; }
+  const int nit = (o_hi - o_lo) * p.nblk;                 // K blocks of this CTA
+  const int ngroups = (nit + kTcFlushBlocks - 1) / kTcFlushBlocks;   // accumulator groups
 
   // ---- set-up: barriers, tensor memory ------------------------------------------------------
   if (tid == 0) {
-    tc_mbar_init(&mbar[0], 1);
-    tc_mbar_init(&mbar[1], 1);
-    tc_mbar_init(flushbar, 1);
+    for (int i = 0; i < kTcStages; ++i) {
+      tc_mbar_init(&full[i], kTcProducerWarps);
+      tc_mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      tc_mbar_init(&accdone[i], 1);
+      tc_mbar_init(&accfree[i], kTcCollectorWarps);
+    }
+    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -269,269 +290,311 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
-  // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
-  const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcBN >> 3) << 17) |
-                         ((uint32_t)(kTcBM >> 4) << 24);
-
-  const int nit = (o_hi - o_lo) * p.nblk;
   bool ok = true;
-
-  // Per-thread staging slots.  The (row, 16-byte chunk) handled by a slot and the part of its
-  // global offset that does not change along K are computed once; the K loop only adds the offset
-  // of block (outer index, slice of the run).  Slots are laid out for the full block width kblk;
-  // chunks past the end of a shorter last slice are staged as zeros.  A contiguous operand maps
-  // consecutive threads to consecutive chunks of one row (coalesced 16-byte loads), a strided one
-  // to consecutive rows (neighbouring 8-byte loads).
-  constexpr int kSlots = kTcBM * (kTcKMax / 4) / kTcThreads;  // 6 for A and 6 for B
-  const int nchf = p.kblk / 4;                                 // chunks per full block
-  long offA[kSlots], offB[kSlots];
-  int soA[kSlots], soB[kSlots], chA[kSlots], chB[kSlots];
-  unsigned oddB = 0;                                           // bit q: slot q stages an "imaginary" column
-  float4 ra[kSlots], rb[kSlots];
-#pragma unroll
-  for (int q = 0; q < kSlots; ++q) {
-    const int e = tid + kTcThreads * q;
-    {
-      int r, ch;
-      if (a_str) { r = e % kTcBM; ch = e / kTcBM; } else { r = e / nchf; ch = e - r * nchf; }
-      const int gr = row0 + r;
-      chA[q] = (r < kTcBM && ch < nchf && gr < M) ? ch : -1;
-      const int ro = gr / RI, ri = gr - ro * RI;
-      long base;
-      if (OP == kTcFwd)        base = ((spec0 + (long)ro * L) * p.nb + ri) * fi2;
-      else if (OP == kTcGradX) base = ((spec0 + (long)ro * L) * p.nb + ri) * fo2;
-      else                       base = (spec0 + ro) * p.nb * fi2 + 2 * ri;
-      offA[q] = base + (a_str ? (long)(2 * ch) * a_st : 4 * ch);
-      soA[q] = ch * kTcLBO + r * 16;
-    }
-    {
-      int rr, ch;
-      if (b_str) { rr = e % kTcBN; ch = e / kTcBN; } else { rr = e / nchf; ch = e - rr * nchf; }
-      const int gcol = col0 + rr;
-      chB[q] = (rr < kTcBN && ch < nchf && gcol < Np) ? ch : -1;
-      const int co = gcol / CW, rem = gcol - co * CW;
-      const int in = rem >> 1;
-      if (rem & 1) oddB |= 1u << q;
-      long base;
-      if (OP == kTcFwd)        base = ((spec0 + (long)co * L) * p.fi * p.fo + in) * 2;
-      else if (OP == kTcGradX) base = ((spec0 + co) * p.fi + in) * fo2;
-      else                       base = (spec0 + co) * p.nb * fo2 + 2 * in;
-      offB[q] = base + (b_str ? (long)(2 * ch) * b_st : 4 * ch);
-      soB[q] = ch * kTcLBO + rr * 16;
-    }
-  }
-
-  auto block_geom = [&](int it, int& oidx, int& k0, int& kvalid) {
-    const int oi = it / p.nblk;
-    const int kb = it - oi * p.nblk;
-    oidx = o_lo + oi;
-    k0 = kb * p.kblk;
-    kvalid = (p.run - k0) < p.kblk ? (p.run - k0) : p.kblk;   // floats with data (even; VEC: multiple of 4)
-  };
-  // four consecutive K floats of one row: (re, im) of two complex numbers; `nvalid` (2 or 4) of them
-  // lie inside the run
-  auto load4 = [&](const float* src, bool strided, long st, int nvalid) {
-    if (VEC && !strided) return __ldg(reinterpret_cast<const float4*>(src));
-    const float2 u = __ldg(reinterpret_cast<const float2*>(src));
-    float2 w = make_float2(0.f, 0.f);
-    if (VEC || nvalid > 2) w = __ldg(reinterpret_cast<const float2*>(src + (strided ? st : 2)));
-    return make_float4(u.x, u.y, w.x, w.y);
-  };
-  auto prefetch = [&](int it) {
-    int oidx, k0, kvalid;
-    block_geom(it, oidx, k0, kvalid);
-    const long pa = (long)oidx * a_ko + (a_str ? (long)(k0 >> 1) * a_st : k0);
-    const long pb = (long)oidx * b_ko + (b_str ? (long)(k0 >> 1) * b_st : k0);
-#pragma unroll
-    for (int q = 0; q < kSlots; ++q) {
-      ra[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (chA[q] >= 0 && 4 * chA[q] < kvalid)
-        ra[q] = load4(p.a + offA[q] + pa, a_str, a_st, kvalid - 4 * chA[q]);
-      rb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (chB[q] >= 0 && 4 * chB[q] < kvalid)
-        rb[q] = load4(p.b + offB[q] + pb, b_str, b_st, kvalid - 4 * chB[q]);
-    }
-  };
-  // v = hi + lo with hi carrying the 10 explicit TF32 mantissa bits (the tensor core ignores the
-  // lower 13 bits of its inputs, so lo = v - hi needs no further rounding)
-  auto split_store = [&](unsigned char* hi_buf, unsigned char* lo_buf, int so, float4 v) {
-    float4 hi, lo;
-    hi.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-    hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-    hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-    hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-    lo.x = v.x - hi.x;
-    lo.y = v.y - hi.y;
-    lo.z = v.z - hi.z;
-    lo.w = v.w - hi.w;
-    *reinterpret_cast<float4*>(hi_buf + so) = hi;
-    *reinterpret_cast<float4*>(lo_buf + so) = lo;
-  };
-  // Real rows of the column operand, per complex number (a, b) of the run:
-  //   fwd, grad y (conjugated operand):  even column (a, b)    odd column (-b, a)
-  //   grad x (plain product):            even column (a, -b)   odd column ( b, a)
-  constexpr bool conj_b = OP != kTcGradX;
-  auto column_rows = [&](float4 v, bool odd) {
-    if (conj_b) return odd ? make_float4(-v.y, v.x, -v.w, v.z) : v;
-    return odd ? make_float4(v.y, v.x, v.w, v.z) : make_float4(v.x, -v.y, v.z, -v.w);
+  // a wait that gives up tells every role to leave its loop
+  auto wait = [&](uint64_t* bar, uint32_t parity) {
+    if (tc_mbar_wait(bar, parity)) return true;
+    *abort_flag = 1;
+    ok = false;
+    return false;
   };
 
-  // This thread's share of an accumulator (TMEM lanes 32 (warp % 4) + lane, 32 columns).  The
-  // accumulator of K-block group g is columns (g & 1) * kTcBN ...; the finished partial sum of a
-  // group is added in FP32 by the threads into the sum region (columns kTcSumCol ...) while the
-  // tensor core works on the next group in the other accumulator.
-  constexpr int kColGroups = kTcThreads / 128;
-  constexpr int kColsPerWarp = kTcBN / kColGroups;
-  static_assert(kColsPerWarp == 32, "one tcgen05.ld of 32 columns per warp");
-  const uint32_t tmem_mine = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16) +
-                             (uint32_t)(kColsPerWarp * (warp >> 2));
-  bool have_sum = false, pending_flush = false;
-  uint32_t flush_parity = 0;
-  bool fresh = true;   // the next MMA starts a new accumulation in tensor memory
-
-  prefetch(0);
-  for (int it = 0; it < nit; ++it) {
-    const int s = it & 1;
-    int oidx, k0, kvalid;
-    block_geom(it, oidx, k0, kvalid);
-    const int ksteps = (kvalid + 7) / 8;
-    unsigned char* stage = smem + (size_t)s * kTcStageBytes;
-    unsigned char* Ahi = stage;
-    unsigned char* Alo = stage + kTcBufBytes;
-    unsigned char* Bhi = stage + 2 * kTcBufBytes;
-    unsigned char* Blo = stage + 3 * kTcBufBytes;
-
-    if (it >= 2) {  // the MMAs that read this stage two iterations ago must have finished
-      if (!tc_mbar_wait(&mbar[s], (uint32_t)((it / 2 - 1) & 1))) ok = false;
+  if (warp == 0) {
+    // ================================ issuer ====================================================
+    // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcBN >> 3) << 17) |
+                           ((uint32_t)(kTcBM >> 4) << 24);
+    // The operand descriptors of every (stage, buffer, k-step) differ from the one of stage 0,
+    // A hi, k-step 0 only in the 14-bit start-address field (bytes >> 4), so they are obtained by
+    // adding constants (the whole staging area is below 256 KB, the field cannot overflow).
+    const uint64_t d0 = tc_smem_desc(tc_smem_u32(smem));
+    constexpr uint64_t kDBuf = kTcBufBytes >> 4, kDStage = kTcStageBytes >> 4, kDStep = (2u * kTcLBO) >> 4;
+    constexpr int kStepsMax = kTcKMax / 8;
+    const int steps_full = (p.kblk + 7) / 8;
+    const int steps_tail = (p.run - (p.nblk - 1) * p.kblk + 7) / 8;
+    int kb = 0, s = 0, g = 0, ing = 0;           // block within its run, stage, group, block within its group
+    uint32_t full_par = 0;                        // parity of the `full` phase of the current round of stages
+    for (int it = 0; it < nit && !*abort_flag; ++it) {
+      if (FLUSH && ing == 0 && g >= 2)            // the collectors are done with this accumulator
+        if (!wait(&accfree[g & 1], (uint32_t)((g / 2 - 1) & 1))) break;
+      if (!wait(&full[s], full_par)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
+      if (lane == 0) {
+        const int ksteps = kb + 1 == p.nblk ? steps_tail : steps_full;
+        const uint64_t da = d0 + (uint64_t)s * kDStage;
+        const uint32_t acc = tmem_base + (FLUSH ? (uint32_t)((g & 1) * kTcBN) : 0u);
 #pragma unroll
-    for (int q = 0; q < kSlots; ++q) {
-      const int e = tid + kTcThreads * q;
-      if (e < kTcBM * nchf) {
-        split_store(Ahi, Alo, soA[q], ra[q]);
-        split_store(Bhi, Blo, soB[q], column_rows(rb[q], (oddB >> q) & 1u));
-      }
-    }
-    if (FLUSH && pending_flush) {
-      if (!tc_mbar_wait(flushbar, flush_parity)) ok = false;
-      flush_parity ^= 1u;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-      // the group that just ended: iteration it - 1, accumulator ((it - 1) / kTcFlushBlocks) & 1
-      const uint32_t done_acc = (uint32_t)((((it - 1) / kTcFlushBlocks) & 1) * kTcBN);
-      for (int h = 0; h < 2; ++h) {       // 16 columns at a time keeps the transient registers low
-        float v[16];
-        tc_ld16(tmem_mine + done_acc + 16 * h, v);
-        if (have_sum) {
-          float w[16];
-          tc_ld16(tmem_mine + kTcSumCol + 16 * h, w);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += w[i];
+        for (int ks = 0; ks < kStepsMax; ++ks) {
+          if (ks < ksteps) {
+            const uint64_t dah = da + ks * kDStep, dal = dah + kDBuf;
+            const uint64_t dbh = dah + 2 * kDBuf, dbl = dah + 3 * kDBuf;
+            tc_mma_tf32(acc, dah, dbh, idesc, (ing == 0 && ks == 0) ? 0u : 1u);
+            tc_mma_tf32(acc, dal, dbh, idesc, 1u);
+            tc_mma_tf32(acc, dah, dbl, idesc, 1u);
+          }
         }
-        tc_st16(tmem_mine + kTcSumCol + 16 * h, v);
+        tc_commit(&empty[s]);     // arrives when these MMAs have read the stage
+        if (ing + 1 == kTcFlushBlocks || it + 1 == nit) tc_commit(&accdone[g & 1]);
       }
-      have_sum = true;
-      // that accumulator is written again kTcFlushBlocks iterations from now, after block barriers
-      // that every thread reaches only once these reads are done
+      __syncwarp();
+      if (++kb == p.nblk) kb = 0;
+      if (++s == kTcStages) { s = 0; full_par ^= 1u; }
+      if (++ing == kTcFlushBlocks) { ing = 0; ++g; }
     }
-    if (it + 1 < nit) prefetch(it + 1);
-    // make the generic-proxy writes visible to the tensor core (async proxy), then hand over
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_hi = tc_smem_u32(Ahi), a_lo = tc_smem_u32(Alo);
-      const uint32_t b_hi = tc_smem_u32(Bhi), b_lo = tc_smem_u32(Blo);
-      const uint32_t acc = tmem_base + (FLUSH ? (uint32_t)(((it / kTcFlushBlocks) & 1) * kTcBN) : 0u);
-      for (int ks = 0; ks < ksteps; ++ks) {
-        const uint32_t koff = (uint32_t)ks * 2u * kTcLBO;
-        const uint64_t dah = tc_smem_desc(a_hi + koff), dal = tc_smem_desc(a_lo + koff);
-        const uint64_t dbh = tc_smem_desc(b_hi + koff), dbl = tc_smem_desc(b_lo + koff);
-        tc_mma_tf32(acc, dah, dbh, idesc, (fresh && ks == 0) ? 0u : 1u);
-        tc_mma_tf32(acc, dal, dbh, idesc, 1u);
-        tc_mma_tf32(acc, dah, dbl, idesc, 1u);
+  } else if (warp <= kTcCollectorWarps) {
+    // ================================ collectors ================================================
+    // This warp's TMEM lane quarter, all 128 columns: every finished accumulator but the last is
+    // added into the sum region while the tensor core fills the other accumulator.
+    if (FLUSH) {
+      const uint32_t lanes = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16);
+      for (int g = 0; g + 1 < ngroups && !*abort_flag; ++g) {
+        if (!wait(&accdone[g & 1], (uint32_t)((g / 2) & 1))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+        for (int h = 0; h < kTcBN / 16; ++h) {   // 16 columns at a time keeps the registers low
+          float v[16];
+          tc_ld16(lanes + (uint32_t)((g & 1) * kTcBN + 16 * h), v);
+          if (g > 0) {
+            float w[16];
+            tc_ld16(lanes + (uint32_t)(kTcSumCol + 16 * h), w);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += w[i];
+          }
+          tc_st16(lanes + (uint32_t)(kTcSumCol + 16 * h), v);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&accfree[g & 1]))
+                       : "memory");
       }
-      tc_commit(&mbar[s]);
     }
-    // every kTcFlushBlocks blocks the issuer moves on to the other accumulator; the finished
-    // partial sum is collected at the top of the next iteration, where the staging registers are free
-    pending_flush = FLUSH && ((it + 1) % kTcFlushBlocks == 0) && (it + 1 < nit);
-    fresh = pending_flush;
-    if (pending_flush && tid == 0) tc_commit(flushbar);   // arrives when every MMA so far has finished
+  } else {
+    // ================================ producers =================================================
+    const int pt = tid - kTcFirstProducer;
+    // operand addressing (floats): offset of outer contraction index `o`, element `kf` of its run =
+    //   contiguous:  o * ko + kf          strided:  o * ko + (kf / 2) * st + (kf % 2)
+    constexpr bool a_str = OP == kTcGradY, b_str = OP != kTcGradX;
+    long a_ko, b_ko, a_st = 0, b_st = 0;
+    if (OP == kTcFwd)        { a_ko = (long)p.nb * fi2;      b_ko = (long)p.fi * fo2;      b_st = fo2; }
+    else if (OP == kTcGradX) { a_ko = (long)p.nb * fo2;      b_ko = (long)L * p.fi * fo2; }
+    else                       { a_ko = (long)L * p.nb * fi2;  b_ko = (long)L * p.nb * fo2;  a_st = fi2; b_st = fo2; }
+
+    // Per-thread staging slots.  Everything that does not change along K is computed once per
+    // slot: the global address of its 16-byte chunk in K block 0 (null for a row, column or chunk
+    // outside the problem), its place in a stage buffer, whether it lies inside the shorter last
+    // block of a run, and for the column operand whether it builds an "imaginary" column.  The K
+    // loop then only adds one running offset per operand (advanced by a constant per block and by
+    // another per outer index - no division, no per-slot geometry).  A contiguous operand maps
+    // consecutive threads to consecutive chunks of one row (coalesced 16-byte loads), a strided one
+    // to consecutive rows (neighbouring 8-byte loads).
+    constexpr int kSlots = kTcBM * (kTcKMax / 4) / kTcProducers;  // 2 for A and 2 for B
+    static_assert(kSlots * kTcProducers == kTcBM * (kTcKMax / 4), "slots per producer");
+    float4 ra0[kSlots], rb0[kSlots], ra1[kSlots], rb1[kSlots];   // two K blocks in flight
+    const int nchf = p.kblk / 4;                                 // chunks per full block
+    const int tail = p.run - (p.nblk - 1) * p.kblk;              // floats of a run's last block (even; VEC: multiple of 4)
+    const float* gA[kSlots];
+    const float* gB[kSlots];
+    int soA[kSlots], soB[kSlots];
+    unsigned tailA = 0, tailB = 0;        // bit q: slot q has data in the last block of a run ...
+    unsigned tailA2 = 0, tailB2 = 0;      // ... but only its first complex number (8-byte variant)
+    unsigned oddB = 0;                    // bit q: slot q stages an "imaginary" column
+    unsigned live = 0;                    // bit q: slot q is written at all (zeros if its pointer is null)
+#pragma unroll
+    for (int q = 0; q < kSlots; ++q) {
+      const int e = pt + kTcProducers * q;
+      if (e < kTcBM * nchf) live |= 1u << q;
+      {
+        int r, ch;
+        if (a_str) { r = e % kTcBM; ch = e / kTcBM; } else { r = e / nchf; ch = e - r * nchf; }
+        const int gr = row0 + r;
+        const bool okA = r < kTcBM && ch < nchf && gr < M;
+        const int ro = gr / RI, ri = gr - ro * RI;
+        long base;
+        if (OP == kTcFwd)        base = ((spec0 + (long)ro * L) * p.nb + ri) * fi2;
+        else if (OP == kTcGradX) base = ((spec0 + (long)ro * L) * p.nb + ri) * fo2;
+        else                       base = (spec0 + ro) * p.nb * fi2 + 2 * ri;
+        base += (long)o_lo * a_ko + (a_str ? (long)(2 * ch) * a_st : 4 * ch);
+        gA[q] = okA ? p.a + base : nullptr;
+        soA[q] = ch * kTcLBO + r * 16;
+        if (4 * ch < tail) tailA |= 1u << q;
+        if (tail - 4 * ch == 2) tailA2 |= 1u << q;
+      }
+      {
+        int rr, ch;
+        if (b_str) { rr = e % kTcBN; ch = e / kTcBN; } else { rr = e / nchf; ch = e - rr * nchf; }
+        const int gcol = col0 + rr;
+        const bool okB = rr < kTcBN && ch < nchf && gcol < Np;
+        const int co = gcol / CW, rem = gcol - co * CW;
+        const int in = rem >> 1;
+        if (rem & 1) oddB |= 1u << q;
+        long base;
+        if (OP == kTcFwd)        base = ((spec0 + (long)co * L) * p.fi * p.fo + in) * 2;
+        else if (OP == kTcGradX) base = ((spec0 + co) * p.fi + in) * fo2;
+        else                       base = (spec0 + co) * p.nb * fo2 + 2 * in;
+        base += (long)o_lo * b_ko + (b_str ? (long)(2 * ch) * b_st : 4 * ch);
+        gB[q] = okB ? p.b + base : nullptr;
+        soB[q] = ch * kTcLBO + rr * 16;
+        if (4 * ch < tail) tailB |= 1u << q;
+        if (tail - 4 * ch == 2) tailB2 |= 1u << q;
+      }
+    }
+    // offsets (floats) from K block 0 to the next block of a run / to block 0 of the next outer index
+    const long a_stepk = a_str ? (long)(p.kblk >> 1) * a_st : p.kblk;
+    const long b_stepk = b_str ? (long)(p.kblk >> 1) * b_st : p.kblk;
+    const long a_stepo = a_ko - (long)(p.nblk - 1) * a_stepk;
+    const long b_stepo = b_ko - (long)(p.nblk - 1) * b_stepk;
+
+    // four consecutive K floats of one row: (re, im) of two complex numbers
+    auto load4 = [&](const float* src, bool strided, long st, bool only_first) {
+      if (VEC && !strided) return __ldg(reinterpret_cast<const float4*>(src));
+      const float2 u = __ldg(reinterpret_cast<const float2*>(src));
+      float2 w = make_float2(0.f, 0.f);
+      if (VEC || !only_first) w = __ldg(reinterpret_cast<const float2*>(src + (strided ? st : 2)));
+      return make_float4(u.x, u.y, w.x, w.y);
+    };
+    // the cursor of the loads runs two K blocks ahead of the one being staged
+    long cur_a = 0, cur_b = 0;
+    int cur_kb = 0;
+    auto prefetch = [&](float4 (&ra)[kSlots], float4 (&rb)[kSlots]) {
+      const bool last = cur_kb + 1 == p.nblk;
+#pragma unroll
+      for (int q = 0; q < kSlots; ++q) {
+        ra[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gA[q] && (!last || ((tailA >> q) & 1u)))
+          ra[q] = load4(gA[q] + cur_a, a_str, a_st, last && ((tailA2 >> q) & 1u));
+        rb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gB[q] && (!last || ((tailB >> q) & 1u)))
+          rb[q] = load4(gB[q] + cur_b, b_str, b_st, last && ((tailB2 >> q) & 1u));
+      }
+      if (last) { cur_kb = 0; cur_a += a_stepo; cur_b += b_stepo; }
+      else { ++cur_kb; cur_a += a_stepk; cur_b += b_stepk; }
+    };
+    // v = hi + lo with hi carrying the 10 explicit TF32 mantissa bits (the tensor core ignores the
+    // lower 13 bits of its inputs, so lo = v - hi needs no further rounding)
+    auto split_store = [&](unsigned char* hi_buf, unsigned char* lo_buf, int so, float4 v) {
+      float4 hi, lo;
+      hi.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+      hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+      hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+      hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+      lo.x = v.x - hi.x;
+      lo.y = v.y - hi.y;
+      lo.z = v.z - hi.z;
+      lo.w = v.w - hi.w;
+      *reinterpret_cast<float4*>(hi_buf + so) = hi;
+      *reinterpret_cast<float4*>(lo_buf + so) = lo;
+    };
+    // Real rows of the column operand, per complex number (a, b) of the run:
+    //   fwd, grad y (conjugated operand):  even column (a, b)    odd column (-b, a)
+    //   grad x (plain product):            even column (a, -b)   odd column ( b, a)
+    constexpr bool conj_b = OP != kTcGradX;
+    auto column_rows = [&](float4 v, bool odd) {
+      if (conj_b) return odd ? make_float4(-v.y, v.x, -v.w, v.z) : v;
+      return odd ? make_float4(v.y, v.x, v.w, v.z) : make_float4(v.x, -v.y, v.z, -v.w);
+    };
+
+    // stage K block `it` from the registers that hold it, then refill them with block it + 2
+    auto stage_block = [&](int it, float4 (&ra)[kSlots], float4 (&rb)[kSlots]) {
+      const int s = it % kTcStages;
+      unsigned char* stage = smem + (size_t)s * kTcStageBytes;
+      if (it >= kTcStages) {  // the MMAs that read this stage kTcStages blocks ago must have finished
+        if (!wait(&empty[s], (uint32_t)((it / kTcStages - 1) & 1))) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+#pragma unroll
+      for (int q = 0; q < kSlots; ++q) {
+        if ((live >> q) & 1u) {
+          split_store(stage, stage + kTcBufBytes, soA[q], ra[q]);
+          split_store(stage + 2 * kTcBufBytes, stage + 3 * kTcBufBytes, soB[q],
+                      column_rows(rb[q], (oddB >> q) & 1u));
+        }
+      }
+      if (it + 2 < nit) prefetch(ra, rb);
+      // make the generic-proxy writes visible to the tensor core (async proxy), then hand over:
+      // one arrival per producer warp
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&full[s])) : "memory");
+      return true;
+    };
+    prefetch(ra0, rb0);
+    if (nit > 1) prefetch(ra1, rb1);
+    for (int it = 0; it < nit && !*abort_flag; it += 2) {
+      if (!stage_block(it, ra0, rb0)) break;
+      if (it + 1 < nit && !stage_block(it + 1, ra1, rb1)) break;
+    }
   }
 
-  // ---- wait for the last commit (it covers every earlier MMA of the issuing thread) ----------
-  {
-    const int last = nit - 1;
-    if (!tc_mbar_wait(&mbar[last & 1], (uint32_t)((last / 2) & 1))) ok = false;
-    if (nit >= 2) {  // drain the other stage's barrier too so no arrival is pending at exit
-      const int prev = nit - 2;
-      if (!tc_mbar_wait(&mbar[prev & 1], (uint32_t)((prev / 2) & 1))) ok = false;
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  // ---- every MMA of this CTA has finished once the last accumulator group has been committed ----
+  // (waited for by the collectors, which have followed every earlier phase of these barriers; the
+  // block barrier below passes the fact on to the other warps)
+  __syncwarp();
+  if (warp >= 1 && warp <= kTcCollectorWarps && !*abort_flag) {
+    const int glast = ngroups - 1;
+    wait(&accdone[glast & 1], (uint32_t)((glast / 2) & 1));
   }
-
-  ok = __syncthreads_and(ok) != 0;  // block-uniform from here on
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  ok = __syncthreads_and(ok && !*abort_flag) != 0;  // block-uniform from here on
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
   // ---- epilogue: TMEM -> registers -> z -----------------------------------------------------
-  if (ok) {
-    // warp w may only touch TMEM lanes 32 (w % 4) .. +31; the warps sharing a lane quarter split
-    // the 128 accumulator columns between them
-    const int q = warp & 3, cg = warp >> 2;
+  if (ok && warp != 0) {
+    // warp w may only touch TMEM lanes 32 (w % 4) .. +31; the four warps sharing a lane quarter
+    // split the 128 accumulator columns between them
+    constexpr int kColsPerWarp = kTcBN / 4;
+    static_assert(kColsPerWarp == 32, "one tcgen05.ld of 32 columns per warp");
+    const int q = warp & 3, cg = (warp - 1) >> 2;
     const int r = row0 + 32 * q + lane;
     const int ro = r / RI, ri = r - ro * RI;
     // c[((spec0 + ro * sro + co * sco) * RI + ri) * CW + rem]
     const int sro = OP == kTcGradY ? 1 : L, sco = OP == kTcGradY ? L : 1;
-#pragma unroll 1
-    const uint32_t last_acc = FLUSH ? (uint32_t)((((nit - 1) / kTcFlushBlocks) & 1) * kTcBN) : 0u;
-    for (int g = 0; g < kColsPerWarp / 32; ++g) {
-      const int cbase = kColsPerWarp * cg + 32 * g;
-      float v[32];
-      tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + last_acc + (uint32_t)cbase, v);
-      if (FLUSH && have_sum) {
-        float w[32];
-        tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTcSumCol + cbase), w);
+    const uint32_t last_acc = FLUSH ? (uint32_t)(((ngroups - 1) & 1) * kTcBN) : 0u;
+    const int cbase = kColsPerWarp * cg;
+    float v[32];
+    tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + last_acc + (uint32_t)cbase, v);
+    if (FLUSH && ngroups > 1) {
+      float w[32];
+      tc_ld32(tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(kTcSumCol + cbase), w);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] += w[i];
-      }
-      if (r < M) {
-        if constexpr (VEC) {
+      for (int i = 0; i < 32; ++i) v[i] += w[i];
+    }
+    if (r < M) {
+      if constexpr (VEC) {
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const int gcol = col0 + cbase + 4 * c4;
-            if (gcol < Np) {  // CW is a multiple of 4, so a group of 4 is all in or all out
-              const int co = gcol / CW, rem = gcol - co * CW;
-              float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
-              if (nsplit > 1) {
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const int gcol = col0 + cbase + 4 * c4;
+          if (gcol < Np) {  // CW is a multiple of 4, so a group of 4 is all in or all out
+            const int co = gcol / CW, rem = gcol - co * CW;
+            float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
+            if (nsplit > 1) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) atomicAdd(dst + u, v[4 * c4 + u]);
-              } else {
-                *reinterpret_cast<float4*>(dst) =
-                    make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
-              }
+              for (int u = 0; u < 4; ++u) atomicAdd(dst + u, v[4 * c4 + u]);
+            } else {
+              *reinterpret_cast<float4*>(dst) =
+                  make_float4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
             }
           }
-        } else {
+        }
+      } else {
 #pragma unroll
-          for (int c2 = 0; c2 < 16; ++c2) {
-            const int gcol = col0 + cbase + 2 * c2;
-            if (gcol < Np) {  // one complex number: never straddles an outer column index
-              const int co = gcol / CW, rem = gcol - co * CW;
-              float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
-              if (nsplit > 1) {
-                atomicAdd(dst, v[2 * c2]);
-                atomicAdd(dst + 1, v[2 * c2 + 1]);
-              } else {
-                *reinterpret_cast<float2*>(dst) = make_float2(v[2 * c2], v[2 * c2 + 1]);
-              }
+        for (int c2 = 0; c2 < 16; ++c2) {
+          const int gcol = col0 + cbase + 2 * c2;
+          if (gcol < Np) {  // one complex number: never straddles an outer column index
+            const int co = gcol / CW, rem = gcol - co * CW;
+            float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
+            if (nsplit > 1) {
+              atomicAdd(dst, v[2 * c2]);
+              atomicAdd(dst + 1, v[2 * c2 + 1]);
+            } else {
+              *reinterpret_cast<float2*>(dst) = make_float2(v[2 * c2], v[2 * c2 + 1]);
             }
           }
         }
       }
     }
-  } else if (tid == 0) {
+  } else if (!ok && tid == 0) {
     atomicExch(p.err, 1);
   }
 
