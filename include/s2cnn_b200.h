@@ -37,6 +37,18 @@ long s2c_launch_count(void);
 /* Frees the cached tables of every device (replaces nothing in the reference; its lru_caches
  * are never cleared). */
 void s2c_clear_tables(void);
+/* On-disk cache of the Wigner tables: `dir` (an existing directory) turns it on, NULL or "" off;
+ * unset, the environment variable S2CNN_B200_TABLE_CACHE is consulted once.  One file per (kind,
+ * bandwidths, weighting), written under a temporary name and renamed into place, verified by a
+ * checksum when read - safe with several processes.  Replaces the reference's cached_dirpklgz
+ * decorator (s2cnn/utils/decorator.py:54-104) around its table builders.  The two counters report
+ * tables read from / written to the directory by this process. */
+void s2c_set_table_cache_dir(const char* dir);
+long s2c_table_cache_hits(void);
+long s2c_table_cache_stores(void);
+/* Number of Wigner tables this process has computed from scratch so far (the host side logs a
+ * message when it grows, as the reference does at s2cnn/soft/so3_fft.py:223, s2_fft.py:127). */
+long s2c_tables_computed(void);
 /* Per-kernel timing for benchmarks (no counterpart in the reference): between begin and end every
  * launch is bracketed by a CUDA event pair on its own stream; end() waits for them and writes one
  * text line per kernel, "<name> <launches> <total_ms>", into buf. */
@@ -215,6 +227,15 @@ int s2c_so3_rotation_matrices(int b, double alpha, double beta, double gamma, fl
  * s2cnn/soft/so3_rotation.py:22-41 (and, with adjoint, its autograd). */
 int s2c_so3_rotate_spectrum(const float* U, const float* x, float* z, int b, long nbatch,
                             int adjoint, void* stream);
+
+/* ---- data preparation of the 3-D shape model --------------------------------------------------- */
+/* Ray-cast projection of a triangle mesh onto sphere grid points: verts [nv][3] float32, faces
+ * [nf][3] int32 (vertex indices, not range-checked), grid [nr][3] ray origins (direction = towards
+ * the origin), all on the device; out [3][nr] = distance to the first hit (1 if none), n . p and
+ * |n x p| with n the hit triangle's unit normal and p the normalised origin (0 if none).  Replaces
+ * render_model, examples/shrec17/dataset.py:53-95 (trimesh / pyembree ray casting on the host). */
+int s2c_project_on_sphere(const float* verts, int nv, const int* faces, int nf, const float* grid,
+                          int nr, float* out, void* stream);
 
 /* ---- test hooks (not part of the drop-in surface; no counterpart in the reference) ------------ */
 /* Path selection for the test-suite, so that every kernel variant can be compared with the oracle

@@ -14,11 +14,13 @@ from .so3_mm import so3_mm
 from .soft import (S2Convolution, SO3Convolution, SO3Shortcut, so3_integrate, so3_relu_integrate,
                    so3_rotation)
 from .fuse import fuse
+from . import models, projection
+from .tables import set_table_cache_dir
 
 __all__ = [
     "s2_rft", "so3_rft", "s2_near_identity_grid", "s2_equatorial_grid", "s2_soft_grid",
     "so3_near_identity_grid", "so3_equatorial_grid", "so3_soft_grid", "s2_mm", "so3_mm",
     "so3_rotation",
     "S2Convolution", "SO3Convolution", "SO3Shortcut", "so3_integrate", "so3_relu_integrate",
-    "fuse",
+    "fuse", "models", "projection", "set_table_cache_dir",
 ]

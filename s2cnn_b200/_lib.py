@@ -23,6 +23,10 @@ _SIGNATURES = {
     "s2c_version": (c_int, []),
     "s2c_launch_count": (c_long, []),
     "s2c_clear_tables": (None, []),
+    "s2c_set_table_cache_dir": (None, [c_char_p]),
+    "s2c_table_cache_hits": (c_long, []),
+    "s2c_table_cache_stores": (c_long, []),
+    "s2c_tables_computed": (c_long, []),
     "s2c_is_cuda_build": (c_int, []),
     "s2c_timing_begin": (None, []),
     "s2c_timing_end": (c_int, [c_char_p, c_size_t]),
@@ -64,6 +68,7 @@ _SIGNATURES = {
     "s2c_so3_integrate_backward": (c_int, [_P, _P, _P, c_long, c_int, c_int, _P]),
     "s2c_so3_rotation_matrices": (c_int, [c_int, c_double, c_double, c_double, _P]),
     "s2c_so3_rotate_spectrum": (c_int, [_P, _P, _P, c_int, c_long, c_int, _P]),
+    "s2c_project_on_sphere": (c_int, [_P, c_int, _P, c_int, _P, c_int, _P, _P]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

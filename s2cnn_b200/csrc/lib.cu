@@ -22,6 +22,7 @@
 #include "s2_mm_thin.h"
 #include "so3_mm_tc.h"
 #include "misc_kernels.h"
+#include "project_kernels.h"
 
 namespace s2c {
 thread_local long g_launch_count = 0;
@@ -356,6 +357,10 @@ const char* s2c_last_error(void) { return last_error_ref().c_str(); }
 int s2c_version(void) { return 100; }
 long s2c_launch_count(void) { return g_launch_count; }
 void s2c_clear_tables(void) { TableCache::get().clear(); }
+void s2c_set_table_cache_dir(const char* dir) { TableDiskCache::get().set_dir(dir); }
+long s2c_table_cache_hits(void) { return TableDiskCache::get().hits(); }
+long s2c_table_cache_stores(void) { return TableDiskCache::get().stores(); }
+long s2c_tables_computed(void) { return TableCache::computed_count().load(); }
 int s2c_is_cuda_build(void) {
 #ifdef S2C_EMUL
   return 0;
@@ -948,6 +953,17 @@ int s2c_so3_integrate_backward(const float* g, const float* x, float* gx, long n
   S2C_TRY(TableCache::get().quad_weights(b, &p.w));
   const long blocks = std::min<long>((p.total + 255) / 256, 148L * 16);
   return S2C_LAUNCH(so3_integrate_bwd, blocks, 256, 0, as_stream(st), p);
+}
+
+int s2c_project_on_sphere(const float* verts, int nv, const int* faces, int nf, const float* grid,
+                          int nr, float* out, void* st) {
+  if (!verts || !faces || !grid || !out || nv < 1 || nf < 1 || nr < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_project_on_sphere: bad argument");
+  ProjectParams p;
+  p.verts = verts; p.faces = faces; p.grid = grid; p.out = out;
+  p.nv = nv; p.nf = nf; p.nr = nr;
+  return S2C_LAUNCH(project_on_sphere, (nr + kProjThreads - 1) / kProjThreads, kProjThreads,
+                    kProjTile * 12 * sizeof(float), as_stream(st), p);
 }
 
 int s2c_so3_rotation_matrices(int b, double alpha, double beta, double gamma, float* out) {

@@ -15,10 +15,14 @@
 // first call for a new (bandwidth, kind, device) therefore allocates and copies synchronously.
 #pragma once
 
+#include <cstdio>
 #include <map>
 #include <memory>
 #include <mutex>
 #include <tuple>
+#ifndef _WIN32
+#include <unistd.h>
+#endif
 
 #include "backend.h"
 #include "host_math.h"
@@ -71,6 +75,112 @@ S2C_HD void so3_pair_decode(int idx, int K, int& m, int& n) {
   else { const int t = idx - K; n = t / (2 * K - 1) + 1; m = t % (2 * K - 1) - (K - 1); }
 }
 
+// ---- optional on-disk cache of the Wigner panel tables ------------------------------------------
+// Plays the role of the reference's `cached_dirpklgz` decorator around its table builders
+// (s2cnn/utils/decorator.py:54-104, used at s2cnn/soft/so3_fft.py:212 and s2_fft.py:116): the host
+// build of a large table (seconds at b = 128) is paid once per machine instead of once per process.
+// Unlike the reference's index.pkl read-modify-write it is safe with several processes: one file per
+// key, written under a temporary name and moved into place with rename(); a reader checks magic,
+// key, sizes and a checksum and rebuilds (and rewrites) the table on any mismatch.  Off unless a
+// directory is given (s2c_set_table_cache_dir, or the environment variable S2CNN_B200_TABLE_CACHE).
+class TableDiskCache {
+ public:
+  static TableDiskCache& get() {
+    static TableDiskCache c;
+    return c;
+  }
+  void set_dir(const char* dir) {
+    std::lock_guard<std::mutex> g(mu_);
+    dir_ = dir ? dir : "";
+    env_checked_ = true;
+  }
+  std::string dir() {
+    std::lock_guard<std::mutex> g(mu_);
+    if (!env_checked_) {
+      const char* e = std::getenv("S2CNN_B200_TABLE_CACHE");
+      if (e) dir_ = e;
+      env_checked_ = true;
+    }
+    return dir_;
+  }
+  long hits() const { return hits_; }
+  long stores() const { return stores_; }
+
+  struct Key {
+    int b_beta, nl, K, weighted, s2;
+  };
+  bool load(const Key& k, std::vector<float>& data, std::vector<long long>& off) {
+    const std::string d = dir();
+    if (d.empty()) return false;
+    FILE* f = std::fopen(path(d, k).c_str(), "rb");
+    if (!f) return false;
+    Header h;
+    bool ok = std::fread(&h, sizeof(h), 1, f) == 1 && h.magic == kMagic && h.version == kVersion &&
+              h.key[0] == k.b_beta && h.key[1] == k.nl && h.key[2] == k.K && h.key[3] == k.weighted &&
+              h.key[4] == k.s2 && h.n_off < (1ull << 32) && h.n_data < (1ull << 34);
+    if (ok) {
+      off.resize((size_t)h.n_off);
+      data.resize((size_t)h.n_data);
+      ok = std::fread(off.data(), sizeof(long long), off.size(), f) == off.size() &&
+           std::fread(data.data(), sizeof(float), data.size(), f) == data.size() &&
+           checksum(data, off) == h.checksum;
+    }
+    std::fclose(f);
+    if (ok) ++hits_;
+    return ok;
+  }
+  void store(const Key& k, const std::vector<float>& data, const std::vector<long long>& off) {
+    const std::string d = dir();
+    if (d.empty()) return;
+    const std::string final_path = path(d, k);
+    char suffix[64];
+    std::snprintf(suffix, sizeof(suffix), ".tmp.%ld.%p", (long)getpid(), (const void*)&data);
+    const std::string tmp = final_path + suffix;
+    FILE* f = std::fopen(tmp.c_str(), "wb");
+    if (!f) return;   // the cache is an optimisation: an unwritable directory is not an error
+    Header h;
+    h.magic = kMagic; h.version = kVersion;
+    h.key[0] = k.b_beta; h.key[1] = k.nl; h.key[2] = k.K; h.key[3] = k.weighted; h.key[4] = k.s2;
+    h.n_off = off.size(); h.n_data = data.size();
+    h.checksum = checksum(data, off);
+    bool ok = std::fwrite(&h, sizeof(h), 1, f) == 1 &&
+              std::fwrite(off.data(), sizeof(long long), off.size(), f) == off.size() &&
+              std::fwrite(data.data(), sizeof(float), data.size(), f) == data.size();
+    ok = (std::fclose(f) == 0) && ok;
+    if (ok && std::rename(tmp.c_str(), final_path.c_str()) == 0) ++stores_;
+    else std::remove(tmp.c_str());
+  }
+
+ private:
+  struct Header {
+    unsigned magic, version;
+    int key[5];
+    int pad;
+    unsigned long long n_off, n_data, checksum;
+  };
+  static constexpr unsigned kMagic = 0x54433253u, kVersion = 1;   // "S2CT"
+  static std::string path(const std::string& dir, const Key& k) {
+    char name[160];
+    std::snprintf(name, sizeof(name), "/wigner_%s_b%d_nl%d_K%d_%s.s2ct", k.s2 ? "s2" : "so3", k.b_beta,
+                  k.nl, k.K, k.weighted ? "quadrature" : "degree");
+    return dir + name;
+  }
+  static unsigned long long checksum(const std::vector<float>& data, const std::vector<long long>& off) {
+    unsigned long long h = 1469598103934665603ull;   // FNV-1a over 64-bit words
+    auto mix = [&](unsigned long long v) { h = (h ^ v) * 1099511628211ull; };
+    for (long long o : off) mix((unsigned long long)o);
+    const size_t n2 = data.size() / 2;
+    const unsigned long long* w = reinterpret_cast<const unsigned long long*>(data.data());
+    for (size_t i = 0; i < n2; ++i) mix(w[i]);
+    if (data.size() & 1) { unsigned u; std::memcpy(&u, &data.back(), 4); mix(u); }
+    return h;
+  }
+  std::mutex mu_;
+  std::string dir_;
+  bool env_checked_ = false;
+  std::atomic<long> hits_{0}, stores_{0};
+};
+
 class TableCache {
  public:
   static TableCache& get() {
@@ -109,9 +219,24 @@ class TableCache {
     return S2C_OK;
   }
 
-  // Host build of the panel table (also exported for tests).
+  // Host build of the panel table, through the on-disk cache when one is configured.
   static void build_panels(int b_beta, int nl, int K, bool weighted, bool s2,
                            std::vector<float>& data, std::vector<long long>& off) {
+    const TableDiskCache::Key key{b_beta, nl, K, (int)weighted, (int)s2};
+    if (TableDiskCache::get().load(key, data, off)) return;
+    compute_panels(b_beta, nl, K, weighted, s2, data, off);
+    ++computed_count();
+    TableDiskCache::get().store(key, data, off);
+  }
+
+  // number of panel tables this process has computed from scratch (not read from the disk cache)
+  static std::atomic<long>& computed_count() {
+    static std::atomic<long> n{0};
+    return n;
+  }
+
+  static void compute_panels(int b_beta, int nl, int K, bool weighted, bool s2,
+                             std::vector<float>& data, std::vector<long long>& off) {
     const int nbeta = 2 * b_beta;
     std::vector<double> beta, w;
     soft_betas(b_beta, beta);

@@ -10,6 +10,9 @@ model is left as traced.  The result computes the same function.
 
     conv_a -> relu -> SO3Convolution b     conv_a(x, relu_so3_fft=b.b_out); b(.., input_spectrum=True)
                                            (synthesis, bias, ReLU and the next analysis in one kernel)
+    conv -> BatchNorm3d (eval mode)        conv(x, channel_scale=s, bias=t): the normalisation is a
+                                           per-channel affine map, folded into the kernel's spectrum
+                                           and the bias (training-mode BatchNorm is left alone)
     SO3Convolution -> relu -> so3_integrate    conv(x, relu_integrate=True)
     relu -> SO3Convolution                 conv(x, relu_input=True)   (ReLU applied while loading)
     relu -> so3_integrate                  so3_relu_integrate(x)
@@ -18,6 +21,7 @@ A chain is only rewritten when the intermediate tensor has no other consumer and
 ones the fused kernels take (2 b <= 32, non-increasing bandwidth); otherwise it stays as it is.
 """
 import sys
+from operator import getitem as _getitem
 
 import torch
 import torch.fx
@@ -73,7 +77,21 @@ class _RecordedCalls:
         return False
 
 
-_OWN_KEYWORDS = {"relu_input", "relu_integrate", "input_spectrum", "relu_so3_fft"}
+_OWN_KEYWORDS = {"relu_input", "relu_integrate", "input_spectrum", "relu_so3_fft", "channel_scale",
+                 "bias"}
+
+
+def _fold_batchnorm(conv_bias, mean, var, weight, bias, eps):
+    """Eval-mode BatchNorm3d after a convolution with bias b:  ((y + b) - mean) / sqrt(var + eps) *
+    weight + bias  =  y * s + (b * s + bias - mean * s): the per-channel scale for the kernel's
+    spectrum and the bias that replaces the layer's own."""
+    s = torch.rsqrt(var + eps)
+    if weight is not None:
+        s = s * weight
+    shift = -mean * s
+    if bias is not None:
+        shift = shift + bias
+    return s, conv_bias * s.view(1, -1, 1, 1, 1) + shift.view(1, -1, 1, 1, 1)
 
 
 def _is_relu(node, modules):
@@ -113,6 +131,29 @@ def fuse(model):
     with _RecordedCalls(so3_integrate, so3_relu_integrate):
         graph = tracer.trace(model)
     modules = dict(model.named_modules())
+    # eval-mode BatchNorm3d right after a convolution: fold it into the layer
+    for node in list(graph.nodes):
+        bn = modules.get(node.target) if node.op == "call_module" else None
+        if not isinstance(bn, torch.nn.BatchNorm3d) or bn.training or bn.running_mean is None:
+            continue
+        src = node.args[0] if node.args else None
+        if not isinstance(src, torch.fx.Node) or len(src.users) != 1:
+            continue
+        conv = _conv(src, modules, (S2Convolution, SO3Convolution))
+        if conv is None or src.kwargs:
+            continue
+        with graph.inserting_before(src):
+            attr = lambda mod_name, name: graph.get_attr(mod_name + "." + name)  # noqa: E731
+            weight = attr(node.target, "weight") if bn.affine else None
+            bias = attr(node.target, "bias") if bn.affine else None
+            folded = graph.call_function(_fold_batchnorm, (
+                attr(src.target, "bias"), attr(node.target, "running_mean"),
+                attr(node.target, "running_var"), weight, bias, bn.eps))
+            scale = graph.call_function(_getitem, (folded, 0))
+            new_bias = graph.call_function(_getitem, (folded, 1))
+        src.kwargs = {"channel_scale": scale, "bias": new_bias}
+        node.replace_all_uses_with(src)
+        graph.erase_node(node)
     for node in list(graph.nodes):
         if not _is_relu(node, modules):
             continue

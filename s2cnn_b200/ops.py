@@ -6,6 +6,7 @@ raw pointers plus the current CUDA stream.  The public, reference-named API in t
 is built on ``cuda_ops()``, which is bound to the CUDA build and refuses CPU tensors.
 """
 import contextlib
+import logging
 import os
 
 import torch
@@ -36,6 +37,16 @@ def _prod(shape):
 class Ops:
     def __init__(self, lib):
         self.lib = lib
+        self._tables_seen = 0
+
+    def _log_new_tables(self, what):
+        """The reference logs "Compute Wigner ..." on the "trainer" logger whenever a table is
+        built (s2cnn/soft/so3_fft.py:223, s2_fft.py:127); same here, from the library's counter."""
+        n = self.lib.s2c_tables_computed()
+        if n != self._tables_seen:
+            logging.getLogger("trainer").info("Compute Wigner tables (%s): %d computed by this process",
+                                              what, n)
+            self._tables_seen = n
 
     # -- helpers -------------------------------------------------------------------------------
     def _prep(self, *tensors):
@@ -80,6 +91,7 @@ class Ops:
             else:
                 self.lib.call("s2c_so3_rfft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
                               int(bool(for_grad)), ws.data_ptr(), ws.numel(), self._stream(x))
+        self._log_new_tables("so3_rfft b %d -> %d" % (b_in, b_out))
         return out.view(-1, *lead, 2)
 
     def so3_fft(self, x, for_grad=False, b_out=None):
@@ -123,6 +135,7 @@ class Ops:
             self.lib.call("s2c_so3_rifft", x.data_ptr(), out.data_ptr(), nbatch, b_in, b_out,
                           int(bool(for_grad)), bias_ptr, nfeat, ws.data_ptr(), ws.numel(),
                           self._stream(x))
+        self._log_new_tables("so3_rifft b %d -> %d" % (b_in, b_out))
         return out.view(*lead, n, n, n)
 
     def so3_rifft_relu_integrate(self, x, bias=None, b_out=None):
@@ -420,6 +433,24 @@ class Ops:
         with self._ctx(x):
             self.lib.call("s2c_so3_rotate_spectrum", U.data_ptr(), x.data_ptr(), out.data_ptr(), b,
                           nbatch, int(adjoint), self._stream(x))
+        return out
+
+    # -- data preparation ----------------------------------------------------------------------
+    def project_on_sphere(self, verts, faces, grid):
+        """verts [nv, 3] float32, faces [nf, 3] int32, grid [nr, 3] float32 -> [3, nr] float32
+        (distance to the first hit, normal . ray, |normal x ray|; see include/s2cnn_b200.h)."""
+        self._prep(verts, grid)
+        if faces.dtype != torch.int32 or faces.is_cuda != self.lib.is_cuda:
+            raise TypeError("faces must be an int32 tensor on the library's device")
+        assert verts.dim() == 2 and verts.size(1) == 3 and faces.dim() == 2 and faces.size(1) == 3
+        assert grid.dim() == 2 and grid.size(1) == 3
+        assert int(faces.min()) >= 0 and int(faces.max()) < verts.size(0), "face index out of range"
+        verts, faces, grid = verts.contiguous(), faces.contiguous(), grid.contiguous()
+        out = verts.new_empty((3, grid.size(0)))
+        with self._ctx(verts):
+            self.lib.call("s2c_project_on_sphere", verts.data_ptr(), verts.size(0), faces.data_ptr(),
+                          faces.size(0), grid.data_ptr(), grid.size(0), out.data_ptr(),
+                          self._stream(verts))
         return out
 
     def so3_ft_matrix(self, b, grid):

@@ -64,13 +64,16 @@ class S2Convolution(Module):
         self.bias = Parameter(torch.zeros(1, nfeature_out, 1, 1, 1))
         self._spectrum_cache = KernelSpectrumCache()
 
-    def forward(self, x, relu_so3_fft=None):
+    def forward(self, x, relu_so3_fft=None, channel_scale=None, bias=None):
         '''
         :x:      [batch, feature_in,  beta, alpha]
         :relu_so3_fft: (extension) bandwidth b_next of the SO3Convolution that follows: return
                  SO3_fft_real(relu(conv(x)), b_next) - that layer's input spectrum
                  [l * m * n, batch, feature_out, complex] (pass it on with ``input_spectrum=True``).
                  Without autograd and for 2 b_out <= 32 the signal between the layers is never written.
+        :channel_scale, bias: (extension, used by ``s2cnn_b200.fuse`` to fold an eval-mode BatchNorm3d
+                 into the layer) multiply output channel j by channel_scale[j] - applied to the
+                 kernel's spectrum - and add ``bias`` ([1, f_out, 1, 1, 1]) instead of the layer's own
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
         assert x.size(1) == self.nfeature_in
@@ -81,10 +84,13 @@ class S2Convolution(Module):
         x = S2_fft_real.apply(x, self.b_out)  # [l * m, batch, feature_in, complex]
         # [l * m, feature_in, feature_out, complex]; kept between calls while the weights stand still
         y = self._spectrum_cache.get(self.kernel, lambda k: s2_rft(k * self.scaling, self.b_out, self.grid))
+        if channel_scale is not None:
+            y = y * channel_scale.view(1, 1, -1, 1)
+        own_bias = self.bias if bias is None else bias
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
             if not needs_grad and 2 * self.b_out <= 32 and b_next <= self.b_out:
-                return cuda_ops().s2_conv_relu_so3_rfft(x, y, self.bias, b_next)
-            return SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(x, y, self.bias)), b_next)
+                return cuda_ops().s2_conv_relu_so3_rfft(x, y, own_bias, b_next)
+            return SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(x, y, own_bias)), b_next)
         # s2_mm -> SO3_ifft_real -> + bias, fused: [batch, feature_out, beta, alpha, gamma]
-        return _S2ProductSynthesis.apply(x, y, self.bias)
+        return _S2ProductSynthesis.apply(x, y, own_bias)

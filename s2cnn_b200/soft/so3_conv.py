@@ -37,7 +37,7 @@ class SO3Convolution(Module):
         self._spectrum_cache = KernelSpectrumCache()
 
     def forward(self, x, relu_input=False, relu_integrate=False, input_spectrum=False,
-                relu_so3_fft=None):
+                relu_so3_fft=None, channel_scale=None, bias=None):
         '''
         :x:      [batch, feature_in,  beta, alpha, gamma]
         :input_spectrum: (extension) x is already SO3_fft_real(signal, b_out), as returned by
@@ -47,6 +47,10 @@ class SO3Convolution(Module):
         :relu_input: (extension) compute conv(relu(x)); the activation is applied while x is read
         :relu_integrate: (extension) return so3_integrate(relu(conv(x))) [batch, feature_out]; without
                          autograd and for 2 b_out <= 32 the output signal is never written
+        :channel_scale, bias: (extension, used by ``s2cnn_b200.fuse`` to fold an eval-mode BatchNorm3d
+                         into the layer) multiply output channel j by channel_scale[j] - applied to
+                         the kernel's spectrum, the layer being linear in it - and add ``bias``
+                         ([1, f_out, 1, 1, 1]) instead of the layer's own
         :return: [batch, feature_out, beta, alpha, gamma]
         '''
         if input_spectrum:
@@ -64,20 +68,23 @@ class SO3Convolution(Module):
                 x = SO3_fft_real.apply(x, self.b_out)  # [l * m * n, batch, feature_in, complex]
         # [l * m * n, feature_in, feature_out, complex]; kept between calls while the weights stand still
         y = self._spectrum_cache.get(self.kernel, lambda k: so3_rft(k * self.scaling, self.b_out, self.grid))
+        if channel_scale is not None:
+            y = y * channel_scale.view(1, 1, -1, 1)
+        own_bias = self.bias if bias is None else bias
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)
         z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
             if (2 * self.b_out <= 32 and b_next <= self.b_out and
-                    not (torch.is_grad_enabled() and (z.requires_grad or self.bias.requires_grad))):
-                return cuda_ops().so3_rifft_relu_rfft(z, self.bias, self.b_out, b_next)
-            return SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(z, self.bias)), b_next)
+                    not (torch.is_grad_enabled() and (z.requires_grad or own_bias.requires_grad))):
+                return cuda_ops().so3_rifft_relu_rfft(z, own_bias, self.b_out, b_next)
+            return SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(z, own_bias)), b_next)
         if relu_integrate:
-            if 2 * self.b_out <= 32 and not (torch.is_grad_enabled() and (z.requires_grad or self.bias.requires_grad)):
-                return cuda_ops().so3_rifft_relu_integrate(z, bias=self.bias)  # [batch, feature_out]
-            return so3_relu_integrate(SO3_ifft_real_bias.apply(z, self.bias))
-        return SO3_ifft_real_bias.apply(z, self.bias)  # [batch, feature_out, beta, alpha, gamma]
+            if 2 * self.b_out <= 32 and not (torch.is_grad_enabled() and (z.requires_grad or own_bias.requires_grad)):
+                return cuda_ops().so3_rifft_relu_integrate(z, bias=own_bias)  # [batch, feature_out]
+            return so3_relu_integrate(SO3_ifft_real_bias.apply(z, own_bias))
+        return SO3_ifft_real_bias.apply(z, own_bias)  # [batch, feature_out, beta, alpha, gamma]
 
 
 class SO3Shortcut(Module):

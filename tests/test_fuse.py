@@ -113,3 +113,50 @@ def test_fuse_leaves_shared_activations_alone(backend):
         x = torch.randn(2, 2, 6, 6, 6).to(dev)
         with torch.no_grad():
             assert_close(fused(x), net(x), "residual model")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_fuse_folds_eval_mode_batchnorm(backend):
+    """conv -> BatchNorm3d -> ReLU -> conv -> BatchNorm3d -> ReLU -> so3_integrate, the layout of the
+    reference's 3-D shape model (examples/shrec17/model.py:17-35): in eval mode the normalisations
+    disappear into the layers and the chains fuse; in training mode nothing is folded."""
+    import s2cnn_b200 as S
+    with backends.active(backend) as (ops, dev):
+        g2 = S.s2_equatorial_grid(max_beta=0, n_alpha=8, n_beta=1)
+        g3 = S.so3_equatorial_grid(max_beta=0, max_gamma=0, n_alpha=8, n_beta=1, n_gamma=1)
+        torch.manual_seed(21)
+
+        class Net(nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.sequential = nn.Sequential(
+                    S.S2Convolution(3, 5, 8, 4, g2), nn.BatchNorm3d(5, affine=True), nn.ReLU(),
+                    S.SO3Convolution(5, 4, 4, 3, g3), nn.BatchNorm3d(4, affine=True), nn.ReLU())
+                self.out_layer = nn.Linear(4, 3)
+
+            def forward(self, x):
+                x = self.sequential(x)
+                x = S.so3_integrate(x)
+                return F.log_softmax(self.out_layer(x), dim=1)
+
+        net = Net()
+        with torch.no_grad():
+            for m in net.modules():
+                if isinstance(m, nn.BatchNorm3d):
+                    m.running_mean.normal_()
+                    m.running_var.uniform_(0.5, 2.0)
+                    m.weight.normal_()
+                    m.bias.normal_()
+                if isinstance(m, (S.S2Convolution, S.SO3Convolution)):
+                    m.bias.normal_()
+        net = net.to(dev)
+        x = torch.randn(3, 3, 16, 16).to(dev)
+        net.train()
+        assert "channel_scale" not in S.fuse(net).code          # batch statistics: not foldable
+        net.eval()
+        fused = S.fuse(net)
+        code = fused.code
+        assert "channel_scale" in code and "relu_so3_fft" in code and "relu_integrate = True" in code
+        assert "sequential_1(" not in code and "sequential_4(" not in code     # no BatchNorm call left
+        with torch.no_grad():
+            assert_close(fused(x), net(x), "model with folded BatchNorm3d")

@@ -425,3 +425,16 @@ def test_bandwidth_32_two_step_fft(backend, b_in, b_out, nbatch):
     finally:
         ops.lib.s2c_debug_force_general_path(0)
         ops.lib.s2c_debug_plane_chunk(0)
+
+
+def test_bandwidth_64_large_path_on_the_emulation_build():
+    """2b = 128 (two betas of the half range per lane in the Wigner kernels, 16-point second FFT
+    step in the plane kernels) through the host-emulation build, one signal: the GPU twin is
+    tests/test_gpu_large_bandwidth.py."""
+    ops, dev = backends.get("emul")
+    gen = torch.Generator().manual_seed(64)
+    x = torch.randn(1, 128, 128, 128, generator=gen)
+    ref = O.so3_rfft(x, b_out=64)
+    got = ops.so3_rfft(x, b_out=64)
+    assert_close(got, ref, "b=64 rfft (emulation)")
+    assert_close(ops.so3_rifft(got), O.so3_rifft(ref), "b=64 rifft (emulation)")
