@@ -24,8 +24,8 @@ inline size_t fwd_wigner_t_smem(int N, int nl) {
 // X[l][z] = sum_beta W[l][beta] V[z][beta]   (+ Hermitian mirror row)
 //
 // The beta range can be processed in kWigHalves pieces with the accumulators kept in registers
-// (less shared memory per block, more blocks per SM); measured on a B200 at b = 64 one piece
-// (0.40 ms) beats two (0.45 ms), so it is 1.  Panel rows and batch rows are staged exactly as they lie in memory (16-byte copies, no transposition): the
+// (less shared memory per block, more blocks per SM); one piece is the faster setting.  Panel rows
+// and batch rows are staged exactly as they lie in memory (16-byte copies, no transposition): the
 // beta loop runs four samples at a time, a thread reads W[l][beta..beta+3] for its four degrees
 // (the whole warp shares the address: broadcast) and V[z][beta..beta+3] for its two batch elements
 // z = tz and tz + ceil(zc/2) (row stride N + 2 complex numbers, so the 8 lanes of a 16-byte access phase

@@ -10,6 +10,7 @@ from ..s2_ft import s2_rft
 from .s2_fft import S2_fft_real
 from .so3_fft import so3_rfft, SO3_fft_real
 from ._spectrum_cache import KernelSpectrumCache
+from ._recompute import fused_or_recompute
 
 
 class _S2ProductSynthesis(torch.autograd.Function):
@@ -79,8 +80,6 @@ class S2Convolution(Module):
         assert x.size(1) == self.nfeature_in
         assert x.size(2) == 2 * self.b_in
         assert x.size(3) == 2 * self.b_in
-        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.kernel.requires_grad or
-                                                  self.bias.requires_grad)
         x = S2_fft_real.apply(x, self.b_out)  # [l * m, batch, feature_in, complex]
         # [l * m, feature_in, feature_out, complex]; kept between calls while the weights stand still
         y = self._spectrum_cache.get(self.kernel, lambda k: s2_rft(k * self.scaling, self.b_out, self.grid))
@@ -89,8 +88,12 @@ class S2Convolution(Module):
         own_bias = self.bias if bias is None else bias
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
-            if not needs_grad and 2 * self.b_out <= 32 and b_next <= self.b_out:
-                return cuda_ops().s2_conv_relu_so3_rfft(x, y, own_bias, b_next)
-            return SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(x, y, own_bias)), b_next)
+            plain = lambda xx, yy, bb: SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(xx, yy, bb)), b_next)  # noqa: E731
+            if 2 * self.b_out <= 32 and b_next <= self.b_out:
+                fused = lambda xx, yy, bb: cuda_ops().s2_conv_relu_so3_rfft(xx, yy, bb, b_next)  # noqa: E731
+                grad = torch.is_grad_enabled() and (x.requires_grad or y.requires_grad or own_bias.requires_grad)
+                return fused_or_recompute(fused, plain, (x, y, own_bias), grad,
+                                          getattr(self, "fused_training", False))
+            return plain(x, y, own_bias)
         # s2_mm -> SO3_ifft_real -> + bias, fused: [batch, feature_out, beta, alpha, gamma]
         return _S2ProductSynthesis.apply(x, y, own_bias)

@@ -12,6 +12,7 @@ from ..so3_mm import so3_mm
 from .so3_fft import SO3_fft_real, SO3_fft_real_relu, SO3_ifft_real_bias
 from .so3_integrate import so3_relu_integrate
 from ._spectrum_cache import KernelSpectrumCache
+from ._recompute import fused_or_recompute
 
 
 class SO3Convolution(Module):
@@ -74,16 +75,21 @@ class SO3Convolution(Module):
         assert x.size(0) == y.size(0)
         assert x.size(2) == y.size(1)
         z = so3_mm(x, y)  # [l * m * n, batch, feature_out, complex]
+        needs_grad = torch.is_grad_enabled() and (z.requires_grad or own_bias.requires_grad)
+        opt_in = getattr(self, "fused_training", False)
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
-            if (2 * self.b_out <= 32 and b_next <= self.b_out and
-                    not (torch.is_grad_enabled() and (z.requires_grad or own_bias.requires_grad))):
-                return cuda_ops().so3_rifft_relu_rfft(z, own_bias, self.b_out, b_next)
-            return SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(z, own_bias)), b_next)
+            plain = lambda zz, bb: SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(zz, bb)), b_next)  # noqa: E731
+            if 2 * self.b_out <= 32 and b_next <= self.b_out:
+                fused = lambda zz, bb: cuda_ops().so3_rifft_relu_rfft(zz, bb, self.b_out, b_next)  # noqa: E731
+                return fused_or_recompute(fused, plain, (z, own_bias), needs_grad, opt_in)
+            return plain(z, own_bias)
         if relu_integrate:
-            if 2 * self.b_out <= 32 and not (torch.is_grad_enabled() and (z.requires_grad or own_bias.requires_grad)):
-                return cuda_ops().so3_rifft_relu_integrate(z, bias=own_bias)  # [batch, feature_out]
-            return so3_relu_integrate(SO3_ifft_real_bias.apply(z, own_bias))
+            plain = lambda zz, bb: so3_relu_integrate(SO3_ifft_real_bias.apply(zz, bb))  # noqa: E731
+            if 2 * self.b_out <= 32:
+                fused = lambda zz, bb: cuda_ops().so3_rifft_relu_integrate(zz, bias=bb)  # noqa: E731
+                return fused_or_recompute(fused, plain, (z, own_bias), needs_grad, opt_in)  # [batch, feature_out]
+            return plain(z, own_bias)
         return SO3_ifft_real_bias.apply(z, own_bias)  # [batch, feature_out, beta, alpha, gamma]
 
 

@@ -160,3 +160,37 @@ def test_fuse_folds_eval_mode_batchnorm(backend):
         assert "sequential_1(" not in code and "sequential_4(" not in code     # no BatchNorm call left
         with torch.no_grad():
             assert_close(fused(x), net(x), "model with folded BatchNorm3d")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_fused_training_recompute_rule_gives_the_same_gradients(backend):
+    """With ``fused_training`` the fused kernels run in a training step too (the signal between the
+    layers is not kept; backward recomputes it through the unfused chain): same loss, same input,
+    kernel and bias gradients as the plain model."""
+    import s2cnn_b200 as S
+    with backends.active(backend) as (ops, dev):
+        torch.manual_seed(31)
+        net, _, _ = _model(S, three=True)
+        net = net.to(dev)
+        x = torch.randn(3, 2, 16, 16).to(dev).requires_grad_(True)
+        net(x).square().sum().backward()
+        want = [x.grad.clone()] + [p.grad.clone() for p in net.parameters()]
+        x.grad = None
+        net.zero_grad()
+        fused = S.fuse(net)
+        for m in net.modules():
+            if isinstance(m, (S.S2Convolution, S.SO3Convolution)):
+                m.fused_training = True
+        n0 = ops.lib.s2c_launch_count()
+        loss = fused(x).square().sum()
+        n_fwd = ops.lib.s2c_launch_count() - n0
+        loss.backward()
+        got = [x.grad.clone()] + [p.grad.clone() for p in net.parameters()]
+        for a, b in zip(got, want):
+            assert_close(a, b, "gradient through the recompute rule")
+        for m in net.modules():
+            if isinstance(m, (S.S2Convolution, S.SO3Convolution)):
+                m.fused_training = False
+        n0 = ops.lib.s2c_launch_count()
+        fused(x)
+        assert n_fwd < ops.lib.s2c_launch_count() - n0     # the training forward really was the fused one
