@@ -203,7 +203,13 @@ int s2c_s2_mm_grady(const float* gz, const float* x, float* gy, int nl, int nbat
  * s2cnn/so3_ft.py:22. */
 int s2c_rft_forward(const float* x, const float* F, float* out, int nf, int n_grid, int nspec,
                     void* stream);
-/* gx[f, a] = sum_{s,c} g[s, f, c] F[a, s, c]: the autograd transpose of the einsum above. */
+/* The same product on the tensor cores (tcgen05, 3xTF32), given the TRANSPOSED matrix
+ * Ft [nspec, 2, n_grid] (the caller keeps it beside F); needs an even n_grid and the CUDA build,
+ * other cases return "unsupported" (use s2c_rft_forward). */
+int s2c_rft_forward_t(const float* x, const float* Ft, float* out, int nf, int n_grid, int nspec,
+                      void* stream);
+/* gx[f, a] = sum_{s,c} g[s, f, c] F[a, s, c]: the autograd transpose of the einsum above (on the
+ * tensor cores when n_grid is even). */
 int s2c_rft_backward(const float* g, const float* F, float* gx, int nf, int n_grid, int nspec,
                      void* stream);
 

@@ -63,6 +63,7 @@ _SIGNATURES = {
     "s2c_s2_mm_gradx": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "s2c_s2_mm_grady": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "s2c_rft_forward": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
+    "s2c_rft_forward_t": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
     "s2c_rft_backward": (c_int, [_P, _P, _P, c_int, c_int, c_int, _P]),
     "s2c_so3_integrate": (c_int, [_P, _P, c_long, c_int, c_int, _P]),
     "s2c_so3_integrate_backward": (c_int, [_P, _P, _P, c_long, c_int, c_int, _P]),

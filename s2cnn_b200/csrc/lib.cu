@@ -817,7 +817,8 @@ static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, in
   const long tiles = so3_mm_tc_tiles(op, nl, nb, fi, fo, p.ksplit);
   // longest K loop of any CTA
   const long lmax = 2 * nl - 1;
-  const bool flush = ((lmax + p.ksplit - 1) / p.ksplit) * p.nblk > kTcFlushBlocks;
+  const long chain_mmas = ((lmax + p.ksplit - 1) / p.ksplit) * (long)((p.run + 7) / 8) * 3;
+  const bool flush = chain_mmas > kTcChainMax;
   const bool vec = so3_mm_tc_vec16(op, nb, fi, fo);
 #define S2C_TC_LAUNCH2(OP, FL, NAME)                                                               \
   (vec ? launch_impl(so3_mm_tc_kernel<OP, FL, true>, NAME, tiles, kTcThreads, kTcSmemBytes, st, p)  \
@@ -826,6 +827,30 @@ static int so3_mm_tc_launch(int op, const float* a, const float* b, float* c, in
   if (op == kTcFwd) return S2C_TC_LAUNCH(kTcFwd, "so3_mm_tc_kernel");
   if (op == kTcGradX) return S2C_TC_LAUNCH(kTcGradX, "so3_mm_tc_gradx");
   return S2C_TC_LAUNCH(kTcGradY, "so3_mm_tc_grady");
+}
+
+// A plain real product C[r][c] = sum_k A[r][k] B[c][k] (M rows, N columns, K terms; N and K even)
+// on the tensor-core pipeline: the kernel-grid -> spectrum transforms and their transposes.
+static int plain_tc_launch(bool a_strided, const float* a, const float* b, float* c, long M, long N,
+                           long K, long a_rs, long a_ps, long b_rs, long b_ps, long c_rs, long c_ps,
+                           stream_t st) {
+  MmTcParams p;
+  p.a = a; p.b = b; p.c = c;
+  p.nl = 1; p.nb = (int)M; p.fi = (int)(K / 2); p.fo = (int)(N / 2);
+  p.run = (int)K;
+  if (p.run <= kTcKMax) { p.kblk = (p.run + 7) / 8 * 8; p.nblk = 1; }
+  else { p.kblk = kTcKMax; p.nblk = (p.run + kTcKMax - 1) / kTcKMax; }
+  p.ksplit = 1;
+  p.a_rs = a_rs; p.a_ps = a_ps; p.b_rs = b_rs; p.b_ps = b_ps; p.c_rs = c_rs; p.c_ps = c_ps;
+  void* flag = nullptr;
+  S2C_TRY(cuda_check(cudaGetSymbolAddress(&flag, g_tc_err_flag), "tensor-core status flag"));
+  p.err = (int*)flag;
+  const long tiles = ((M + kTcBM - 1) / kTcBM) * ((N + kTcBN - 1) / kTcBN);
+  const bool flush = (long)((p.run + 7) / 8) * 3 > kTcChainMax;
+  // 16-byte loads need K a multiple of 4 and 16-byte aligned rows of every contiguous operand
+  const bool vec = K % 4 == 0 && b_rs % 4 == 0 && (a_strided || a_rs % 4 == 0);
+  if (a_strided) return S2C_TC_LAUNCH(kTcPlainSC, "rft_tc_backward");
+  return S2C_TC_LAUNCH(kTcPlainCC, "rft_tc_forward");
 #undef S2C_TC_LAUNCH2
 #undef S2C_TC_LAUNCH
 }
@@ -921,9 +946,28 @@ int s2c_rft_forward(const float* x, const float* F, float* out, int nf, int ng, 
   return S2C_LAUNCH(rft_forward, p.tiles_f * tiles_s, 256, sm, as_stream(st), p);
 }
 
+int s2c_rft_forward_t(const float* x, const float* Ft, float* out, int nf, int ng, int ns, void* st) {
+  if (!x || !Ft || !out || nf < 1 || ng < 1 || ns < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_rft_forward_t: bad argument");
+#ifndef S2C_EMUL
+  if (ng % 2 == 0) {
+    // C[f][(s, c)] = sum_a x[f][a] Ft[(s, c)][a], written to out[s][f][c]
+    return plain_tc_launch(false, x, Ft, out, nf, 2L * ns, ng, ng, 2, ng, 2, 2, 2L * nf, as_stream(st));
+  }
+#endif
+  return fail(S2C_ERR_UNSUPPORTED, "s2c_rft_forward_t: needs the CUDA build and an even n_grid");
+}
+
 int s2c_rft_backward(const float* g, const float* F, float* gx, int nf, int ng, int ns, void* st) {
   if (!g || !F || !gx || nf < 1 || ng < 1 || ns < 1)
     return fail(S2C_ERR_BAD_ARG, "s2c_rft_backward: bad argument");
+#ifndef S2C_EMUL
+  if (!g_force_general && ng % 2 == 0) {
+    // gx[f][a] = sum_{(s, c)} g[s][f][c] F[a][(s, c)]: the row operand holds k = (s, c) as pairs
+    // 2 nf floats apart
+    return plain_tc_launch(true, g, F, gx, nf, ng, 2L * ns, 2, 2L * nf, 2L * ns, 2, ng, 2, as_stream(st));
+  }
+#endif
   RftBwdParams p;
   p.g = (const float2*)g; p.F = (const float2*)F; p.gx = gx;
   p.nf = nf; p.ng = ng; p.ns = ns;

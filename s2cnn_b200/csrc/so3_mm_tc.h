@@ -61,7 +61,12 @@ namespace s2c {
 // an output column (outer, 2 * inner + re/im).  The contraction index is (outer, run of `run`
 // floats): a "contiguous" operand holds the run of a row as consecutive floats (16-byte loads), a
 // "strided" one holds it as complex pairs `stride` floats apart (two 8-byte loads per chunk).
-enum TcOp : int { kTcFwd = 0, kTcGradX = 1, kTcGradY = 2 };
+//   kTcPlainCC / kTcPlainSC: a plain real product C[r][c] = sum_k A[r][k] B[c][k] on the same
+//   pipeline, with explicit strides (rows, pairs of consecutive k, pairs of consecutive c) instead
+//   of the spectral geometry: the kernel-grid -> spectrum transforms s2_rft / so3_rft and their
+//   transposes (s2cnn/s2_ft.py:22, s2cnn/so3_ft.py:22).  CC: both operands hold k contiguously;
+//   SC: the row operand holds k as pairs `a_ps` floats apart.
+enum TcOp : int { kTcFwd = 0, kTcGradX = 1, kTcGradY = 2, kTcPlainCC = 3, kTcPlainSC = 4 };
 
 struct MmTcParams {
   const float* a;   // operand read along the output rows
@@ -74,6 +79,10 @@ struct MmTcParams {
   int ksplit;       // CTAs sharing one output tile (each takes a slice of the outer contraction
                     // index and adds its partial result atomically into the zeroed output); 1 = none
   int* err;         // device flag, set to 1 on a wait time-out
+  // plain products only (floats): element (row r, k) of a at r * a_rs + (k / 2) * a_ps + k % 2,
+  // element (column c, k) of b likewise, element (r, c) of the result at r * c_rs + (c / 2) * c_ps + c % 2;
+  // nb = rows, fi = K / 2, fo = columns / 2, nl = 1
+  long a_rs, a_ps, b_rs, b_ps, c_rs, c_ps;
 };
 
 // row / column geometry of one degree
@@ -104,6 +113,9 @@ constexpr int kTcThreads = 32 * (1 + kTcCollectorWarps + kTcProducerWarps);
 // into the sum region (bounds the length of the tensor core's own accumulation chain, whose
 // additions truncate): 8 blocks = 72 MMAs per chain.
 constexpr int kTcFlushBlocks = 8;
+// longest chain (in MMAs) left to the tensor core's own accumulation without partial sums: its
+// truncation bias stays below about 1e-5 relative
+constexpr int kTcChainMax = 200;
 // tensor-memory columns: two alternating accumulators and the FP32 sum region (power of two)
 constexpr int kTcTmemCols = 512;
 constexpr int kTcSumCol = 2 * kTcBN;
@@ -222,8 +234,8 @@ __host__ __device__ __forceinline__ long tc_tiles_for(int op, int nb, int fi, in
   return ((M + kTcBM - 1) / kTcBM) * ((N + kTcBN - 1) / kTcBN);
 }
 
-// FLUSH = false drops the partial-sum code; valid while no CTA needs more than kTcFlushBlocks K
-// blocks.
+// FLUSH = false keeps the whole chain in one tensor-memory accumulator and drops the partial-sum
+// code; the host selects it while no CTA issues more than kTcChainMax MMAs.
 // VEC = true: 16-byte loads and stores (feature counts - for grad y the batch - even); VEC = false:
 // 8-byte accesses, any sizes.
 template <int OP, bool FLUSH, bool VEC>
@@ -262,7 +274,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
   const long spec0 = (long)l * (4L * l * l - 1) / 3;
   const int fi2 = 2 * p.fi, fo2 = 2 * p.fo;
   const int nit = (o_hi - o_lo) * p.nblk;                 // K blocks of this CTA
-  const int ngroups = (nit + kTcFlushBlocks - 1) / kTcFlushBlocks;   // accumulator groups
+  // accumulator groups (one when the whole chain stays in the tensor core's accumulator)
+  const int ngroups = FLUSH ? (nit + kTcFlushBlocks - 1) / kTcFlushBlocks : 1;
 
   // ---- set-up: barriers, tensor memory ------------------------------------------------------
   if (tid == 0) {
@@ -328,18 +341,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
           if (ks < ksteps) {
             const uint64_t dah = da + ks * kDStep, dal = dah + kDBuf;
             const uint64_t dbh = dah + 2 * kDBuf, dbl = dah + 3 * kDBuf;
-            tc_mma_tf32(acc, dah, dbh, idesc, (ing == 0 && ks == 0) ? 0u : 1u);
+            tc_mma_tf32(acc, dah, dbh, idesc, ((FLUSH ? ing == 0 : it == 0) && ks == 0) ? 0u : 1u);
             tc_mma_tf32(acc, dal, dbh, idesc, 1u);
             tc_mma_tf32(acc, dah, dbl, idesc, 1u);
           }
         }
         tc_commit(&empty[s]);     // arrives when these MMAs have read the stage
-        if (ing + 1 == kTcFlushBlocks || it + 1 == nit) tc_commit(&accdone[g & 1]);
+        if ((FLUSH && ing + 1 == kTcFlushBlocks) || it + 1 == nit) tc_commit(&accdone[g & 1]);
       }
       __syncwarp();
       if (++kb == p.nblk) kb = 0;
       if (++s == kTcStages) { s = 0; full_par ^= 1u; }
-      if (++ing == kTcFlushBlocks) { ing = 0; ++g; }
+      if (FLUSH && ++ing == kTcFlushBlocks) { ing = 0; ++g; }
     }
   } else if (warp <= kTcCollectorWarps) {
     // ================================ collectors ================================================
@@ -374,11 +387,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     const int pt = tid - kTcFirstProducer;
     // operand addressing (floats): offset of outer contraction index `o`, element `kf` of its run =
     //   contiguous:  o * ko + kf          strided:  o * ko + (kf / 2) * st + (kf % 2)
-    constexpr bool a_str = OP == kTcGradY, b_str = OP != kTcGradX;
+    constexpr bool plain = OP == kTcPlainCC || OP == kTcPlainSC;
+    constexpr bool a_str = OP == kTcGradY || OP == kTcPlainSC, b_str = OP == kTcFwd || OP == kTcGradY;
     long a_ko, b_ko, a_st = 0, b_st = 0;
     if (OP == kTcFwd)        { a_ko = (long)p.nb * fi2;      b_ko = (long)p.fi * fo2;      b_st = fo2; }
     else if (OP == kTcGradX) { a_ko = (long)p.nb * fo2;      b_ko = (long)L * p.fi * fo2; }
-    else                       { a_ko = (long)L * p.nb * fi2;  b_ko = (long)L * p.nb * fo2;  a_st = fi2; b_st = fo2; }
+    else if (OP == kTcGradY) { a_ko = (long)L * p.nb * fi2;  b_ko = (long)L * p.nb * fo2;  a_st = fi2; b_st = fo2; }
+    else                       { a_ko = 0; b_ko = 0; a_st = p.a_ps; b_st = p.b_ps; }   // one outer index
 
     // Per-thread staging slots.  Everything that does not change along K is computed once per
     // slot: the global address of its 16-byte chunk in K block 0 (null for a row, column or chunk
@@ -413,7 +428,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
         long base;
         if (OP == kTcFwd)        base = ((spec0 + (long)ro * L) * p.nb + ri) * fi2;
         else if (OP == kTcGradX) base = ((spec0 + (long)ro * L) * p.nb + ri) * fo2;
-        else                       base = (spec0 + ro) * p.nb * fi2 + 2 * ri;
+        else if (OP == kTcGradY) base = (spec0 + ro) * p.nb * fi2 + 2 * ri;
+        else                       base = (long)gr * p.a_rs;
         base += (long)o_lo * a_ko + (a_str ? (long)(2 * ch) * a_st : 4 * ch);
         gA[q] = okA ? p.a + base : nullptr;
         soA[q] = ch * kTcLBO + r * 16;
@@ -431,7 +447,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
         long base;
         if (OP == kTcFwd)        base = ((spec0 + (long)co * L) * p.fi * p.fo + in) * 2;
         else if (OP == kTcGradX) base = ((spec0 + co) * p.fi + in) * fo2;
-        else                       base = (spec0 + co) * p.nb * fo2 + 2 * in;
+        else if (OP == kTcGradY) base = (spec0 + co) * p.nb * fo2 + 2 * in;
+        else                       base = (long)gcol * p.b_rs;
         base += (long)o_lo * b_ko + (b_str ? (long)(2 * ch) * b_st : 4 * ch);
         gB[q] = okB ? p.b + base : nullptr;
         soB[q] = ch * kTcLBO + rr * 16;
@@ -490,6 +507,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     //   grad x (plain product):            even column (a, -b)   odd column ( b, a)
     constexpr bool conj_b = OP != kTcGradX;
     auto column_rows = [&](float4 v, bool odd) {
+      if (plain) return v;
       if (conj_b) return odd ? make_float4(-v.y, v.x, -v.w, v.z) : v;
       return odd ? make_float4(v.y, v.x, v.w, v.z) : make_float4(v.x, -v.y, v.z, -v.w);
     };
@@ -560,7 +578,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] += w[i];
     }
-    if (r < M) {
+    if (r < M && (OP == kTcPlainCC || OP == kTcPlainSC)) {
+#pragma unroll
+      for (int c2 = 0; c2 < 16; ++c2) {
+        const int gcol = col0 + cbase + 2 * c2;
+        if (gcol < Np)
+          *reinterpret_cast<float2*>(p.c + (long)r * p.c_rs + (long)(gcol >> 1) * p.c_ps) =
+              make_float2(v[2 * c2], v[2 * c2 + 1]);
+      }
+    } else if (r < M) {
       if constexpr (VEC) {
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {

@@ -370,6 +370,21 @@ class Ops:
                           ns, self._stream(x2d))
         return out
 
+    def rft_forward_t(self, x2d, Ft):
+        """The same product on the tensor cores: x2d [nf, n_grid], Ft [nspec, 2, n_grid] (the
+        transposed Fourier matrix) -> [nspec, nf, 2].  CUDA build, even n_grid."""
+        self._prep(x2d, Ft)
+        nf, ng = x2d.shape
+        assert Ft.size(2) == ng and Ft.size(1) == 2
+        ns = Ft.size(0)
+        x2d = x2d.contiguous()
+        Ft = Ft.contiguous()
+        out = x2d.new_empty((ns, nf, 2))
+        with self._ctx(x2d):
+            self.lib.call("s2c_rft_forward_t", x2d.data_ptr(), Ft.data_ptr(), out.data_ptr(), nf, ng,
+                          ns, self._stream(x2d))
+        return out
+
     def rft_backward(self, g, F):
         """g [nspec, nf, 2], F [n_grid, nspec, 2] -> [nf, n_grid]"""
         self._prep(g, F)

@@ -87,3 +87,37 @@ def test_so3_mm_gradients_on_tensor_cores(nl, nb, fi, fo):
         lib.s2c_debug_force_general_path(0)
     assert_close(gx, gx_simt, "grad x: tcgen05 vs FP32 kernel")
     assert_close(gy, gy_simt, "grad y: tcgen05 vs FP32 kernel")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nf,ng,b,so3", [(20, 24, 10, False), (800, 192, 6, True), (600, 24, 16, False),
+                                         (130, 192, 10, True), (7, 2, 3, True), (64, 128, 5, True)])
+def test_kernel_transform_on_tensor_cores_matches_fp32_kernel_and_oracle(nf, ng, b, so3):
+    """s2_rft / so3_rft as a plain real product on the tcgen05 pipeline (forward with the transposed
+    Fourier matrix, backward with the row operand read as strided pairs) against the FP32 kernels and
+    a float64 einsum; sizes: the bench layers, the deep model's first layer, ragged tiles, a two-point
+    grid, an equatorial ring of 128 points."""
+    from s2cnn_b200 import _lib
+    from s2cnn_b200.ops import cuda_ops
+    ops = cuda_ops()
+    ns = n3(b) if so3 else b * b
+    gen = torch.Generator().manual_seed(nf + ng)
+    x = torch.randn(nf, ng, generator=gen)
+    F = torch.randn(ng, ns, 2, generator=gen)
+    g = torch.randn(ns, nf, 2, generator=gen)
+    want = torch.einsum("fa,asc->sfc", x.double(), F.double()).float()
+    want_b = torch.einsum("sfc,asc->fa", g.double(), F.double()).float()
+    xd, Fd, gd = x.cuda(), F.cuda(), g.cuda()
+    Ft = Fd.permute(1, 2, 0).contiguous()
+    got = ops.rft_forward_t(xd, Ft)
+    got_b = ops.rft_backward(gd, Fd)
+    torch.cuda.synchronize()
+    assert _lib.cuda_lib().s2c_so3_mm_tc_status() == 0
+    assert_close(got, want, "rft forward on tensor cores")
+    assert_close(got_b, want_b, "rft backward on tensor cores")
+    assert_close(ops.rft_forward(xd, Fd), want, "rft forward FP32 kernel")
+    _lib.cuda_lib().s2c_debug_force_general_path(1)
+    try:
+        assert_close(ops.rft_backward(gd, Fd), want_b, "rft backward FP32 kernel")
+    finally:
+        _lib.cuda_lib().s2c_debug_force_general_path(0)
