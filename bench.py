@@ -494,7 +494,9 @@ def deep_model(device):
             x = torch.relu(self.c3(x))
             return self.lin(S.so3_integrate(x))
 
-    return Deep().to(device)
+    # written with plain calls; fuse() folds every ReLU into the kernel that consumes it (in a
+    # training step the activations are still stored - only the separate ReLU passes disappear)
+    return S.fuse(Deep().to(device))
 
 
 def train_step_c4(device, world, rank, batch=32, steps=60):

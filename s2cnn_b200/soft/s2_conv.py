@@ -8,7 +8,7 @@ from torch.nn.parameter import Parameter
 from ..ops import cuda_ops
 from ..s2_ft import s2_rft
 from .s2_fft import S2_fft_real
-from .so3_fft import so3_rfft, SO3_fft_real
+from .so3_fft import so3_rfft, SO3_fft_real, SO3_fft_real_relu
 from ._spectrum_cache import KernelSpectrumCache
 from ._recompute import fused_or_recompute
 
@@ -88,7 +88,10 @@ class S2Convolution(Module):
         own_bias = self.bias if bias is None else bias
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
-            plain = lambda xx, yy, bb: SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(xx, yy, bb)), b_next)  # noqa: E731
+            if 2 * self.b_out <= 32:   # ReLU applied while the next layer's analysis reads the signal
+                plain = lambda xx, yy, bb: SO3_fft_real_relu.apply(_S2ProductSynthesis.apply(xx, yy, bb), b_next)  # noqa: E731
+            else:
+                plain = lambda xx, yy, bb: SO3_fft_real.apply(torch.relu(_S2ProductSynthesis.apply(xx, yy, bb)), b_next)  # noqa: E731
             if 2 * self.b_out <= 32 and b_next <= self.b_out:
                 fused = lambda xx, yy, bb: cuda_ops().s2_conv_relu_so3_rfft(xx, yy, bb, b_next)  # noqa: E731
                 grad = torch.is_grad_enabled() and (x.requires_grad or y.requires_grad or own_bias.requires_grad)

@@ -79,7 +79,10 @@ class SO3Convolution(Module):
         opt_in = getattr(self, "fused_training", False)
         if relu_so3_fft is not None:
             b_next = int(relu_so3_fft)
-            plain = lambda zz, bb: SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(zz, bb)), b_next)  # noqa: E731
+            if 2 * self.b_out <= 32:   # ReLU applied while the next layer's analysis reads the signal
+                plain = lambda zz, bb: SO3_fft_real_relu.apply(SO3_ifft_real_bias.apply(zz, bb), b_next)  # noqa: E731
+            else:
+                plain = lambda zz, bb: SO3_fft_real.apply(torch.relu(SO3_ifft_real_bias.apply(zz, bb)), b_next)  # noqa: E731
             if 2 * self.b_out <= 32 and b_next <= self.b_out:
                 fused = lambda zz, bb: cuda_ops().so3_rifft_relu_rfft(zz, bb, self.b_out, b_next)  # noqa: E731
                 return fused_or_recompute(fused, plain, (z, own_bias), needs_grad, opt_in)

@@ -75,7 +75,7 @@ class SO3_fft_real_relu(torch.autograd.Function):
     def backward(ctx, grad_output):  # pylint: disable=W
         (x,) = ctx.saved_tensors
         g = so3_rifft(grad_output.contiguous(), for_grad=True, b_out=ctx.b_in)
-        return g * (x > 0).to(g.dtype), None
+        return torch.ops.aten.threshold_backward(g, x, 0), None   # g where x > 0, one pass
 
 
 class SO3_ifft_real(torch.autograd.Function):
