@@ -91,12 +91,23 @@ class Lib:
             fn.restype = res
             fn.argtypes = args
         self.is_cuda = bool(self.cdll.s2c_is_cuda_build())
+        self._nvtx = self.is_cuda and os.environ.get("S2CNN_B200_NVTX", "0") not in ("", "0")
 
     def last_error(self):
         return self.cdll.s2c_last_error().decode()
 
     def call(self, name, *args):
-        rc = getattr(self.cdll, name)(*args)
+        """One library entry point; with S2CNN_B200_NVTX=1 on a CUDA build the call sits inside an
+        NVTX range of the same name (the kernels it launches nest under it in a profiler trace)."""
+        if self._nvtx:
+            import torch
+            torch.cuda.nvtx.range_push(name)
+            try:
+                rc = getattr(self.cdll, name)(*args)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        else:
+            rc = getattr(self.cdll, name)(*args)
         if rc != 0:
             raise S2cError("%s failed (status %d): %s" % (name, rc, self.last_error()))
 

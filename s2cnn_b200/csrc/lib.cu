@@ -121,7 +121,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
   if (b_out > b_in && mode == kSo3Real)  // rows with |m| or |n| >= b_in stay zero (so3_fft.py:44-48)
     S2C_TRY(dev_memset_async(out, 0, (size_t)so3_nspec(b_out) * nbatch * sizeof(float2), st));
   if (!g_force_general && N <= kFusedMaxN &&
-      fused_smem_bytes(N, pan.nrows) <= (size_t)dev_smem_limit() - 1024) {
+      fwd_fused_smem_bytes(N, pan.nrows) <= (size_t)dev_smem_limit() - 1024) {
     FwdFusedParams f;
     f.x = x; f.in_stride = in_stride; f.in_off = in_off;
     f.out = out; f.out_zstride = nbatch;
@@ -130,8 +130,9 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     f.nrows = pan.nrows; f.mode = mode; f.relu = relu;
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
-    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_fwd_fused, kN, grid, 256,
-                                        fused_smem_bytes(N, pan.nrows), st, f));
+    const size_t sm = fwd_fused_smem_bytes(N, pan.nrows);
+    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_fwd_fused, kN, grid,
+                                        fused_threads(sm, (size_t)dev_smem_limit()), sm, st, f));
     return rc;
   }
   if (relu) return fail(S2C_ERR_UNSUPPORTED, "fused ReLU input needs the small-bandwidth path");
@@ -256,8 +257,9 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     }
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
-    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_inv_fused, kN, grid, 256,
-                                        fused_smem_bytes(N, pan.nrows), st, f));
+    const size_t sm = fused_smem_bytes(N, pan.nrows);
+    S2C_DISPATCH_N(N, rc = S2C_LAUNCH_N(so3_inv_fused, kN, grid,
+                                        fused_threads(sm, (size_t)dev_smem_limit()), sm, st, f));
     return rc;
   }
   if (integral)

@@ -221,6 +221,43 @@ struct so3_inv_fused_impl {
       const int grp = bg0 / p.BG;
       const bool landed = bulk_wait(ctx, wbar, (unsigned)(grp & 1));
       const float* wslice = landed ? Wg : p.pan.data_g + (size_t)grp * p.pan.g_stride;
+      if (p.BG == 4 && ZG == 4) {
+        // groups of four betas: one frequency pair per work item with all 4 x 4 (beta, batch
+        // element) accumulators in registers - three 16-byte loads feed 32 multiply-adds
+        for (int pr = ctx.tid; pr < p.pan.npairs; pr += ctx.nthr) {
+          const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
+          const float4* w4 = reinterpret_cast<const float4*>(wslice + info.x * 4);
+          const float4* x4 = reinterpret_cast<const float4*>(Xh + info.x * ZG);
+          float2 s[4][ZG];
+#pragma unroll
+          for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) s[bi][z] = make_float2(0.f, 0.f);
+          for (int li = 0; li < info.y; ++li) {
+            const float4 w = w4[li], xa = x4[2 * li], xb = x4[2 * li + 1];
+            const float wv[4] = {w.x, w.y, w.z, w.w};
+            const float2 xv[ZG] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w),
+                                   make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
+#pragma unroll
+            for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+              for (int z = 0; z < ZG; ++z) {
+                s[bi][z].x = fmaf(wv[bi], xv[z].x, s[bi][z].x);
+                s[bi][z].y = fmaf(wv[bi], xv[z].y, s[bi][z].y);
+              }
+          }
+          float2* pl = planes + info.z * KP + info.w;
+          const bool mirror = (info.w == 0 && info.z > 0);  // n = 0, m > 0: row N - m holds the conjugate
+#pragma unroll
+          for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) {
+              float2* dst = pl + (size_t)(z * 4 + bi) * plane_sz;
+              dst[0] = s[bi][z];
+              if (mirror) dst[(N - 2 * info.z) * KP] = make_float2(s[bi][z].x, -s[bi][z].y);
+            }
+        }
+      } else
       for (int it = ctx.tid; it < p.pan.npairs * bc; it += ctx.nthr) {
         const int pr = it / bc, bi = it - pr * bc;
         const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
@@ -460,6 +497,47 @@ struct so3_fwd_fused_impl {
       ctx.sync();
       // ---- accumulate the Wigner contraction over the betas of this group: one panel row
       //      (l, m, n) per thread, all ZG batch elements -----------------------------------------
+      if (p.BG == 4 && N % 4 == 0) {
+        // four betas per group: the row's four table values are one 16-byte load, fetched (with the
+        // row's indices) one pass ahead of their use so that the latency of global memory overlaps
+        // the multiply-adds of the pass before
+        int r = ctx.tid;
+        int packed = 0;
+        float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < p.nrows) {
+          packed = p.pan.rowmap[r];
+          w4 = *reinterpret_cast<const float4*>(p.pan.data + (long)r * N + bg0);
+        }
+        while (r < p.nrows) {
+          const int rn = r + ctx.nthr;
+          int packed_n = 0;
+          float4 w4n = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (rn < p.nrows) {
+            packed_n = p.pan.rowmap[rn];
+            w4n = *reinterpret_cast<const float4*>(p.pan.data + (long)rn * N + bg0);
+          }
+          int l, m, n;
+          rowmap_unpack(packed, l, m, n);
+          const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
+          const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+          float2 a[ZG];
+#pragma unroll
+          for (int z = 0; z < ZG; ++z) a[z] = acc[r * ZG + z];
+#pragma unroll
+          for (int bi = 0; bi < 4; ++bi)
+#pragma unroll
+            for (int z = 0; z < ZG; ++z) {
+              const float2 xv = src[(size_t)(z * 4 + bi) * plane_sz];
+              a[z].x = fmaf(wv[bi], xv.x, a[z].x);
+              a[z].y = fmaf(wv[bi], xv.y, a[z].y);
+            }
+#pragma unroll
+          for (int z = 0; z < ZG; ++z) acc[r * ZG + z] = a[z];
+          r = rn;
+          packed = packed_n;
+          w4 = w4n;
+        }
+      } else
       for (int r = ctx.tid; r < p.nrows; r += ctx.nthr) {
         int l, m, n;
         rowmap_unpack(p.pan.rowmap[r], l, m, n);
@@ -510,13 +588,13 @@ struct so3_fwd_fused_impl {
 
 #ifndef S2C_EMUL
 template <int N>
-__global__ void __launch_bounds__(256) so3_inv_fused(const InvFusedParams p) {
+__global__ void __launch_bounds__(kFusedMaxThreads) so3_inv_fused(const InvFusedParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
   so3_inv_fused_impl<N>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
 }
 template <int N>
-__global__ void __launch_bounds__(256) so3_fwd_fused(const FwdFusedParams p) {
+__global__ void __launch_bounds__(kFusedMaxThreads) so3_fwd_fused(const FwdFusedParams p) {
   extern __shared__ float4 s2c_dyn_smem[];
   Ctx ctx{(int)threadIdx.x, (int)blockDim.x, (int)blockIdx.x, (int)gridDim.x};
   so3_fwd_fused_impl<N>::run(ctx, p, reinterpret_cast<unsigned char*>(s2c_dyn_smem));
@@ -579,6 +657,17 @@ inline size_t fused_smem_bytes(int N, int nrows) {
   return (size_t)N * sizeof(float2) + (size_t)nrows * kFusedZG * sizeof(float2) +
          (size_t)so3_npairs(K) * sizeof(int4) + ((size_t)nrows * fused_bg(N) + 4) * sizeof(float) + 16 +
          (size_t)kFusedZG * fused_bg(N) * (N * fused_kp(N) + 16) * sizeof(float2);
+}
+// the analysis keeps no pair list and no table slice in shared memory
+inline size_t fwd_fused_smem_bytes(int N, int nrows) {
+  return (size_t)N * sizeof(float2) + (size_t)nrows * kFusedZG * sizeof(float2) +
+         (size_t)kFusedZG * fused_bg(N) * (N * fused_kp(N) + 16) * sizeof(float2);
+}
+// Threads per block: 256 cover one transform per thread in every FFT phase; when the block's
+// shared memory leaves room for only one block per SM anyway, 512 threads halve the passes of the
+// Wigner phases and of the spectrum load / store loops.
+inline int fused_threads(size_t smem_bytes, size_t smem_limit) {
+  return 2 * (smem_bytes + 1024) > smem_limit ? kFusedMaxThreads : 256;
 }
 
 }  // namespace s2c

@@ -57,6 +57,7 @@ struct PanelsDev {
 constexpr int kFusedZG = 4;    // batch elements per block
 constexpr int kMaxBG = 8;      // upper bound of the betas per group
 constexpr int kFusedMaxN = 32;
+constexpr int kFusedMaxThreads = 512;
 // Betas per group: the largest divisor of N that keeps the per-group transform count
 // (ZG * BG * N/2 threads, one transform each) within one pass of a 256-thread block.
 inline int fused_bg(int N) {

@@ -41,7 +41,11 @@ def test_so3_transforms_golden(backend, name):
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b_in,b_out,nbatch", [(1, 1, 1), (1, 3, 2), (3, 1, 5), (13, 7, 1),
-                                               (6, 6, 37), (8, 8, 3), (5, 12, 2)])
+                                               (6, 6, 37), (8, 8, 3), (5, 12, 2),
+                                               # groups of four betas (2b = 24, 28, 32); at 2b = 32
+                                               # the single-kernel path runs 512-thread blocks
+                                               (12, 12, 5), (14, 9, 4), (16, 16, 5), (16, 10, 6),
+                                               (10, 16, 3)])
 def test_so3_transforms_oracle(backend, b_in, b_out, nbatch):
     ops, dev = backends.get(backend)
     gen = torch.Generator().manual_seed(100 * b_in + b_out)
