@@ -539,10 +539,24 @@ def train_step_c4(device, world, rank, batch=32, steps=60):
         return max_over_ranks(a.elapsed_time(e) / steps, world, device), loss
 
     ms_local, loss = timed(False)
+    # one more step with a CUDA-event pair around every launch of the library: where the step goes
+    import ctypes
+    from s2cnn_b200 import _lib
+    lib = _lib.cuda_lib()
+    lib.s2c_timing_begin()
+    step(False)
+    torch.cuda.synchronize()
+    cbuf = ctypes.create_string_buffer(1 << 16)
+    lib.call("s2c_timing_end", cbuf, len(cbuf))
+    rows = [ln.split() for ln in cbuf.value.decode().splitlines() if ln.strip()]
+    rows.sort(key=lambda r: -float(r[2]))
+    kernels = {r[0]: {"launches": int(r[1]), "ms": round(float(r[2]), 4)} for r in rows[:10]}
+    kernels_ms = sum(float(r[2]) for r in rows)
     out = {"workload": "deep model 6->100->100->255->55, b 64->16->10->5, batch %d per rank, "
                        "fwd+bwd" % batch,
            "steps": steps, "n_ranks": world, "global_batch": batch * world,
            "ms_per_step_no_allreduce": ms_local, "grad_bytes": grad_bytes,
+           "library_kernels_ms": round(kernels_ms, 4), "kernels": kernels,
            "loss_finite": bool(torch.isfinite(loss))}
     if world > 1:
         import torch.distributed as dist
