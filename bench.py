@@ -735,7 +735,8 @@ def run_ours(args):
             for i in range(M):
                 pipe.prefetch(x_host[(i + 1) % host_n])   # batch i + 1 -> the idle input buffer
                 pipe.run(out_host)                        # batch i: replay + logits to host memory
-            pipe.join_uploads()        # the interval ends when the last upload has landed, too
+            pipe.join_uploads()        # the interval ends when the last upload has landed, too,
+            pipe.join_results()        # and the last result has reached the host
             e.record()
             e.synchronize()
             e2e_ms += a.elapsed_time(e)
@@ -750,7 +751,8 @@ def run_ours(args):
            "h2d_bytes_per_step": in_bytes * M, "d2h_bytes_per_step": out_host.numel() * 4 * M,
            "ms_per_step": e2e_ms, "ms_per_batch": e2e_ms / M,
            "how": ("upload of the next batch overlapped with the forward pass (two input buffers, "
-                   "copy stream); every batch is uploaded, run and read back inside the interval")
+                   "copy stream; results return on a third stream); every batch is uploaded, run "
+                   "and read back inside the interval")
                   if use_graph else "upload, forward, read-back one after another",
            "serial_ms_per_batch": serial_ms / M, "host_buffers": numa}
 

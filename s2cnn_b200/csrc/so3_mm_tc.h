@@ -100,7 +100,7 @@ __host__ __device__ __forceinline__ TcGeom tc_geom(int op, int nb, int fi, int f
 constexpr int kTcBM = 128, kTcBN = 128;
 constexpr int kTcKMax = 24;                       // floats per K block
 constexpr int kTcStages = 4;
-constexpr int kTcLBO = kTcBM * 16 + 16;           // bytes between K-adjacent core matrices (padded)
+constexpr int kTcLBO = kTcBM * 16 + 64;           // bytes between K-adjacent core matrices (padded)
 constexpr int kTcSBO = 128;                       // bytes between row-adjacent core matrices
 constexpr int kTcBufBytes = (kTcKMax / 4) * kTcLBO;   // one operand buffer (hi or lo)
 constexpr int kTcStageBytes = 4 * kTcBufBytes;        // A hi, A lo, B hi, B lo
@@ -225,6 +225,16 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const float (&v)[16]) {
         "r"(r[15])
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Staging slot e of a contiguous operand -> (row, 16-byte chunk of the K block): groups of 8 slots
+// cover 4 rows x 2 adjacent chunks, consecutive groups the chunk pairs of the same 4 rows (nchf,
+// the chunks per block, is even).
+__device__ __forceinline__ void tc_slot_contiguous(int e, int nchf, int& r, int& ch) {
+  const int g = e >> 3, u = e & 7, npair = nchf >> 1;
+  const int rq = g / npair, cp = g - rq * npair;
+  r = 4 * rq + (u >> 1);
+  ch = 2 * cp + (u & 1);
 }
 
 __host__ __device__ __forceinline__ long tc_tiles_for(int op, int nb, int fi, int fo, int l) {
@@ -400,9 +410,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     // outside the problem), its place in a stage buffer, whether it lies inside the shorter last
     // block of a run, and for the column operand whether it builds an "imaginary" column.  The K
     // loop then only adds one running offset per operand (advanced by a constant per block and by
-    // another per outer index - no division, no per-slot geometry).  A contiguous operand maps
-    // consecutive threads to consecutive chunks of one row (coalesced 16-byte loads), a strided one
-    // to consecutive rows (neighbouring 8-byte loads).
+    // another per outer index - no division, no per-slot geometry).  A strided operand maps
+    // consecutive threads to consecutive rows of one chunk (neighbouring 8-byte loads; 32 lanes store
+    // 512 contiguous bytes).  A contiguous operand maps every 8 consecutive threads to 4 rows x 2
+    // adjacent chunks: each row's two chunks are one 32-byte sector of global memory, consecutive
+    // groups of 8 walk along the same rows, and with chunk columns 128 * 16 + 64 bytes apart the 8
+    // 16-byte stores of a quarter warp fall into 8 different bank groups.
     constexpr int kSlots = kTcBM * (kTcKMax / 4) / kTcProducers;  // 2 for A and 2 for B
     static_assert(kSlots * kTcProducers == kTcBM * (kTcKMax / 4), "slots per producer");
     float4 ra0[kSlots], rb0[kSlots], ra1[kSlots], rb1[kSlots];   // two K blocks in flight
@@ -421,7 +434,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
       if (e < kTcBM * nchf) live |= 1u << q;
       {
         int r, ch;
-        if (a_str) { r = e % kTcBM; ch = e / kTcBM; } else { r = e / nchf; ch = e - r * nchf; }
+        if (a_str) { r = e % kTcBM; ch = e / kTcBM; } else { tc_slot_contiguous(e, nchf, r, ch); }
         const int gr = row0 + r;
         const bool okA = r < kTcBM && ch < nchf && gr < M;
         const int ro = gr / RI, ri = gr - ro * RI;
@@ -438,7 +451,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
       }
       {
         int rr, ch;
-        if (b_str) { rr = e % kTcBN; ch = e / kTcBN; } else { rr = e / nchf; ch = e - rr * nchf; }
+        if (b_str) { rr = e % kTcBN; ch = e / kTcBN; } else { tc_slot_contiguous(e, nchf, rr, ch); }
         const int gcol = col0 + rr;
         const bool okB = rr < kTcBN && ch < nchf && gcol < Np;
         const int co = gcol / CW, rem = gcol - co * CW;

@@ -42,8 +42,9 @@ class PipelinedForward:
 
     Two captured copies of the forward pass (``GraphedForward``) alternate; a copy stream uploads
     batch i + 1 into the idle copy's input buffer while the compute stream replays the graph on
-    batch i and returns its result to pinned host memory.  ``submit`` never blocks the host;
-    ``wait`` blocks until everything submitted so far has reached the host.
+    batch i; a third stream returns each result to pinned host memory, so that the small
+    device-to-host copy does not sit between two replays on the compute stream.  ``submit`` never
+    blocks the host; ``wait`` blocks until everything submitted so far has reached the host.
 
         pipe = PipelinedForward(net, example_device_batch)
         for x_host, y_host in zip(batches, results):      # pinned tensors
@@ -57,8 +58,10 @@ class PipelinedForward:
         self.device = dev
         self.slots = [GraphedForward(module, example_input) for _ in range(depth)]
         self.copy_stream = torch.cuda.Stream(device=dev)
+        self.read_stream = torch.cuda.Stream(device=dev)
         self.uploaded = [torch.cuda.Event() for _ in range(depth)]
         self.consumed = [torch.cuda.Event() for _ in range(depth)]   # slot's input buffer is free again
+        self.returned = [torch.cuda.Event() for _ in range(depth)]   # slot's result has reached the host
         self.n_uploaded = 0
         self.n_run = 0
 
@@ -79,17 +82,29 @@ class PipelinedForward:
             slot = (self.n_uploaded - 1) % len(self.slots)
             torch.cuda.current_stream(self.device).wait_event(self.uploaded[slot])
 
+    def join_results(self):
+        """Make the current stream wait for the most recent read-back (so that an event recorded
+        next on the current stream also covers every result copied so far)."""
+        if self.n_run:
+            slot = (self.n_run - 1) % len(self.slots)
+            torch.cuda.current_stream(self.device).wait_event(self.returned[slot])
+
     def run(self, y_host):
         """Forward pass on the oldest uploaded batch; the result is copied into ``y_host`` (pinned)
-        asynchronously on the current stream."""
+        asynchronously on the read-back stream."""
         assert self.n_run < self.n_uploaded, "run() without a prefetched batch"
         slot = self.n_run % len(self.slots)
         cur = torch.cuda.current_stream(self.device)
         cur.wait_event(self.uploaded[slot])
+        if self.n_run >= len(self.slots):
+            cur.wait_event(self.returned[slot])    # the slot's previous result has left its buffer
         g = self.slots[slot]
         g.graph.replay()
         self.consumed[slot].record(cur)
-        y_host.copy_(g.static_out, non_blocking=True)
+        self.read_stream.wait_event(self.consumed[slot])
+        with torch.cuda.stream(self.read_stream):
+            y_host.copy_(g.static_out, non_blocking=True)
+            self.returned[slot].record(self.read_stream)
         self.n_run += 1
 
     def submit(self, x_host, y_host):
