@@ -9,11 +9,14 @@ Linear(40->10)  on synthetic batches of 256 N(0,1) signals on the 60x60 sphere g
 random-init weights, float32, written as plain module calls and rewritten into the fused kernels by
 ``s2cnn_b200.fuse``.  One step = ``batches_per_step`` forward passes, each over one batch taken in
 turn from a pool of resident batches larger than L2 (a single pass lasts 0.3 ms; a step is sized so
-that the timed region lasts about half a second).  The headline metric is samples/s; ``value`` is
-measured with the batches resident in HBM, ``e2e`` through the public module API from pinned host
-memory (host->device copy of every batch and device->host read of its logits inside the timed
-interval; the copy of batch i+1 runs on a copy stream behind the forward pass of batch i -
-``serial_ms_per_batch`` gives the same without the overlap).
+that the timed region lasts about half a second).  Successive batches are independent, so
+``--lanes`` (default 4) captured copies of the pass replay on their own streams with successive
+batches on successive streams: the blocks of one pass fill the SMs that the partly filled last
+waves of another leave idle (``--lanes 1``: one stream, one pass at a time).  The headline metric
+is samples/s; ``value`` is measured with the batches resident in HBM, ``e2e`` through the public
+module API from pinned host memory (host->device copy of every batch and device->host read of its
+logits inside the timed interval; uploads run on a copy stream ahead of the passes, results return
+on another stream - ``serial_ms_per_batch`` gives the same one after another on one stream).
 
 Further objects on the same line:
   ``so3_fft_b64``     (rank 0, N = 1) the standalone SO(3) FFT round trip at b = 64 (real
@@ -588,18 +591,29 @@ def train_step_c4(device, world, rank, batch=32, steps=60):
     return out
 
 
-def strong_scaling(device, world, rank, net, flush, steps, batches_per_step):
-    """BASELINE config 3 as written: a FIXED global batch of 256 split over the ranks."""
+def strong_scaling(device, world, rank, net, flush, steps, batches_per_step, lanes=1):
+    """BASELINE config 3 as written: a FIXED global batch of 256 split over the ranks (successive
+    global batches on `lanes` alternating streams, as in the headline measurement)."""
     from s2cnn_b200 import parallel
-    from s2cnn_b200.graph import GraphedForward
+    from s2cnn_b200.graph import GraphedForward, InterleavedForward
     lo, hi = parallel.shard_range(BATCH_PER_GPU, rank, world)
     b = hi - lo
     gen = torch.Generator().manual_seed(7)
     x = torch.randn(BATCH_PER_GPU, NET["f0"], 2 * NET["b0"], 2 * NET["b0"], generator=gen)[lo:hi]
     x = x.to(device)
-    g = GraphedForward(net, x)
-    for _ in range(3):
-        g(x)
+    g = InterleavedForward(net, x, lanes=lanes) if lanes > 1 else GraphedForward(net, x)
+
+    def run_batches(n):
+        if lanes > 1:
+            g.fork()
+            for _ in range(n):
+                g.submit(x)
+            g.join()
+        else:
+            for _ in range(n):
+                g(x)
+
+    run_batches(2 * lanes + 1)
     torch.cuda.synchronize()
     barrier(world)
     total = 0.0
@@ -607,14 +621,14 @@ def strong_scaling(device, world, rank, net, flush, steps, batches_per_step):
         flush.zero_()
         a, e = event_pair()
         a.record()
-        for _ in range(batches_per_step):
-            g(x)
+        run_batches(batches_per_step)
         e.record()
         e.synchronize()
         total += a.elapsed_time(e)
     ms = max_over_ranks(total, world, device) / (steps * batches_per_step)
     return {"workload": "net_b30_10_6, global batch 256 split over the ranks",
             "batch_per_gpu": b, "ms_per_batch": ms, "samples_per_s": BATCH_PER_GPU / (ms * 1e-3),
+            "passes_in_flight": lanes,
             "limiter": "launch latency and partly filled SMs: at %d samples per GPU the five "
                        "kernels of a pass have fewer blocks than the GPU has SM slots" % b}
 
@@ -645,9 +659,10 @@ def run_ours(args):
     out_host = torch.empty(B, NET["nclass"]).pin_memory()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
-    from s2cnn_b200.graph import GraphedForward, PipelinedForward
+    from s2cnn_b200.graph import GraphedForward, InterleavedForward, PipelinedForward
     use_graph = not args.no_graph
     graphed = GraphedForward(net, pool[0]) if use_graph else None
+    lanes = InterleavedForward(net, pool[0], lanes=args.lanes) if use_graph and args.lanes > 1 else None
 
     def forward_resident(i):
         if use_graph:
@@ -656,6 +671,12 @@ def run_ours(args):
             return net(pool[i % pool_n])
 
     def step_resident():
+        if lanes is not None:      # successive batches on alternating streams, two passes in flight
+            lanes.fork()
+            for i in range(M):
+                lanes.submit(pool[i % pool_n])
+            lanes.join()
+            return
         for i in range(M):
             forward_resident(i)
 
@@ -720,7 +741,8 @@ def run_ours(args):
         # the same batches with the upload of batch i + 1 running behind the forward pass of batch i
         # (s2cnn_b200.graph.PipelinedForward): every timed interval holds M forward passes, M result
         # read-backs and M uploads; the L2 flush stays between intervals
-        pipe = PipelinedForward(net, pool[0])
+        # one slot more than passes in flight, so that an upload never waits for a running pass
+        pipe = PipelinedForward(net, pool[0], depth=max(2, args.lanes + 1))
         for i in range(3):
             pipe.submit(x_host[i % host_n], out_host)
         pipe.wait()
@@ -750,9 +772,10 @@ def run_ours(args):
     e2e = {"value": B * M * world / (e2e_ms * 1e-3), "unit": "samples/s",
            "h2d_bytes_per_step": in_bytes * M, "d2h_bytes_per_step": out_host.numel() * 4 * M,
            "ms_per_step": e2e_ms, "ms_per_batch": e2e_ms / M,
-           "how": ("upload of the next batch overlapped with the forward pass (two input buffers, "
-                   "copy stream; results return on a third stream); every batch is uploaded, run "
-                   "and read back inside the interval")
+           "how": ("uploads overlapped with the forward passes (%d input buffers, copy stream; each "
+                   "buffer's pass replays on its own stream; results return on another stream); "
+                   "every batch is uploaded, run and read back inside the interval"
+                   % max(2, args.lanes + 1))
                   if use_graph else "upload, forward, read-back one after another",
            "serial_ms_per_batch": serial_ms / M, "host_buffers": numa}
 
@@ -818,7 +841,10 @@ def run_ours(args):
     cfg.update({
         "fusion": "s2_mm + conv1 synthesis + ReLU + conv2 analysis in one kernel; second ReLU and "
                   "so3_integrate inside conv2's synthesis kernel (s2cnn_b200.fuse on a plain Sequential)",
-        "launch": "eager" if args.no_graph else "CUDA graph replay (s2cnn_b200.graph.GraphedForward)",
+        "launch": "eager" if args.no_graph else (
+            "CUDA graph replay (s2cnn_b200.graph.GraphedForward)" if args.lanes < 2 else
+            "CUDA graph replays on %d streams, successive batches on alternating streams "
+            "(s2cnn_b200.graph.InterleavedForward)" % args.lanes),
         "sharding": "batch over ranks, no collective in forward",
         "l2": "inputs rotate through a pool of %d resident batches (%d MB > L2); 256 MB flush "
               "write between timed steps" % (pool_n, pool_n * in_bytes >> 20)})
@@ -835,7 +861,8 @@ def run_ours(args):
     if not args.skip_train:
         extras["train_step_c4"] = train_step_c4(device, world, rank)
     if world > 1 and not args.skip_train:
-        extras["strong_scaling"] = strong_scaling(device, world, rank, net, flush, args.steps, M)
+        extras["strong_scaling"] = strong_scaling(device, world, rank, net, flush, args.steps, M,
+                                                  lanes=args.lanes if use_graph else 1)
     if rank == 0:
         line["clocks"] = clocks
         line.update(extras)
@@ -858,6 +885,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batches-per-step", type=int, default=80,
                     help="forward passes (batches) inside one timed step")
+    ap.add_argument("--lanes", type=int, default=4,
+                    help="forward passes in flight on separate streams (1 = one stream)")
     ap.add_argument("--skip-fft64", action="store_true")
     ap.add_argument("--skip-train", action="store_true",
                     help="omit the training-step and strong-scaling legs")

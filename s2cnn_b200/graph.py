@@ -36,14 +36,58 @@ class GraphedForward:
         return self.static_out
 
 
+class InterleavedForward:
+    """Throughput mode for resident inputs: ``lanes`` captured copies of the forward pass replay on
+    their own streams, successive batches going to successive lanes.  The kernels of one pass depend
+    on each other and each ends with a partly filled last wave of blocks; with two passes in flight
+    the blocks of one fill the SMs the other leaves idle.
+
+        fwd = InterleavedForward(net, example_device_batch)
+        fwd.fork()                          # lanes start after the work already on this stream
+        for x in batches:
+            lane = fwd.submit(x)            # fwd.output(lane) is valid after fwd.join() (or after
+        fwd.join()                          # the lane's next-but-one submit has not yet happened)
+    """
+
+    def __init__(self, module, example_input, lanes=2):
+        assert lanes >= 1
+        dev = example_input.device
+        self.device = dev
+        self.slots = [GraphedForward(module, example_input) for _ in range(lanes)]
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)]
+        self.done = [torch.cuda.Event() for _ in range(lanes)]
+        self.n = 0
+
+    def fork(self):
+        cur = torch.cuda.current_stream(self.device)
+        for st in self.streams:
+            st.wait_stream(cur)
+
+    def submit(self, x):
+        lane = self.n % len(self.slots)
+        with torch.cuda.stream(self.streams[lane]):
+            self.slots[lane](x)
+            self.done[lane].record(self.streams[lane])
+        self.n += 1
+        return lane
+
+    def output(self, lane):
+        return self.slots[lane].static_out
+
+    def join(self):
+        cur = torch.cuda.current_stream(self.device)
+        for ev in self.done:
+            cur.wait_event(ev)
+
+
 class PipelinedForward:
     """Inference on batches that arrive in pinned host memory, with the host-to-device copy of the
     next batch overlapped with the forward pass of the current one.
 
-    Two captured copies of the forward pass (``GraphedForward``) alternate; a copy stream uploads
-    batch i + 1 into the idle copy's input buffer while the compute stream replays the graph on
-    batch i; a third stream returns each result to pinned host memory, so that the small
-    device-to-host copy does not sit between two replays on the compute stream.  ``submit`` never
+    Two captured copies of the forward pass (``GraphedForward``) alternate, each on its own compute
+    stream (so the tail of one pass overlaps the head of the next); a copy stream uploads batch
+    i + 1 into the idle copy's input buffer while batch i runs; another stream returns each result
+    to pinned host memory, so that the small device-to-host copy does not sit between two replays.  ``submit`` never
     blocks the host; ``wait`` blocks until everything submitted so far has reached the host.
 
         pipe = PipelinedForward(net, example_device_batch)
@@ -59,6 +103,7 @@ class PipelinedForward:
         self.slots = [GraphedForward(module, example_input) for _ in range(depth)]
         self.copy_stream = torch.cuda.Stream(device=dev)
         self.read_stream = torch.cuda.Stream(device=dev)
+        self.compute = [torch.cuda.Stream(device=dev) for _ in range(depth)]   # one per slot
         self.uploaded = [torch.cuda.Event() for _ in range(depth)]
         self.consumed = [torch.cuda.Event() for _ in range(depth)]   # slot's input buffer is free again
         self.returned = [torch.cuda.Event() for _ in range(depth)]   # slot's result has reached the host
@@ -94,13 +139,15 @@ class PipelinedForward:
         asynchronously on the read-back stream."""
         assert self.n_run < self.n_uploaded, "run() without a prefetched batch"
         slot = self.n_run % len(self.slots)
-        cur = torch.cuda.current_stream(self.device)
-        cur.wait_event(self.uploaded[slot])
+        st = self.compute[slot]      # the slots replay on their own streams: two passes in flight
+        st.wait_stream(torch.cuda.current_stream(self.device))
+        st.wait_event(self.uploaded[slot])
         if self.n_run >= len(self.slots):
-            cur.wait_event(self.returned[slot])    # the slot's previous result has left its buffer
+            st.wait_event(self.returned[slot])     # the slot's previous result has left its buffer
         g = self.slots[slot]
-        g.graph.replay()
-        self.consumed[slot].record(cur)
+        with torch.cuda.stream(st):
+            g.graph.replay()
+            self.consumed[slot].record(st)
         self.read_stream.wait_event(self.consumed[slot])
         with torch.cuda.stream(self.read_stream):
             y_host.copy_(g.static_out, non_blocking=True)
