@@ -104,6 +104,14 @@ int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, in
 int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,
                   const float* bias, int nfeature, void* workspace, size_t workspace_bytes,
                   void* stream);
+/* Backward of "so3_rfft(relu(a))" with respect to a, in one kernel:
+ *   out = so3_rifft(x, for_grad = 1, b_out) where act > 0, else 0
+ * x [nspec(b_in), nbatch, 2] = gradient of the spectrum, act [nbatch, 2b_out, 2b_out, 2b_out] = the
+ * signal the forward pass read, out of the same shape.  Only for 2 b_out <= 32 (single-kernel path);
+ * other sizes return "unsupported".  Replaces the backward of SO3_fft_real (s2cnn/soft/so3_fft.py:
+ * 453-456: so3_ifft(for_grad=True), real part) followed by the backward of F.relu. */
+int s2c_so3_rifft_relu_grad(const float* x, const float* act, float* out, long nbatch, int b_in,
+                            int b_out, void* stream);
 /* so3_integrate(relu(so3_rifft(x) + bias)) without writing the signal: out [nbatch] - the tail
  * "SO3Convolution -> ReLU -> so3_integrate" of the reference's classifiers (e.g.
  * examples/mnist/run.py:88-97) in the synthesis kernel.  Only for 2 b_out <= 32 (single-kernel

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "s2c_debug_plane_chunk": (None, [c_int]),
     "s2c_so3_fft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
     "s2c_so3_rifft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P, c_size_t, _P]),
+    "s2c_so3_rifft_relu_grad": (c_int, [_P, _P, _P, c_long, c_int, c_int, _P]),
     "s2c_so3_rifft_relu_integrate": (c_int, [_P, _P, c_long, c_int, c_int, _P, c_int, _P]),
     "s2c_s2_conv_relu_so3_rfft": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P]),
     "s2c_so3_rifft_relu_rfft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_int, _P]),

@@ -227,7 +227,8 @@ static bool so3_synthesis_is_fused(int b_in, int b_out) {
 static int so3_synthesis(const float2* x, float* out, long out_stride, long out_off, long nbatch,
                          int b_in, int b_out, bool weighted, int mode, const float* bias,
                          int nfeat, void* ws, size_t ws_bytes, stream_t st,
-                         const S2ProductArgs* prod = nullptr, float* integral = nullptr) {
+                         const S2ProductArgs* prod = nullptr, float* integral = nullptr,
+                         const float* mask = nullptr) {
   const int N = 2 * b_out, K = std::min(b_in, b_out);
   FftDev fft;
   PanelsDev pan;
@@ -244,6 +245,9 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     f.nrows = pan.nrows; f.mode = mode;
     f.xs = nullptr; f.ys = nullptr; f.s2_nb = f.s2_fin = f.s2_fout = 0;
     f.iw = nullptr; f.isum = nullptr;
+    f.mask = mask;
+    if (mask && (out_stride != 1 || out_off != 0))
+      return fail(S2C_ERR_UNSUPPORTED, "masked synthesis: real output only");
     if (integral) {
       if (N % f.BG != 0 || kFusedZG * f.BG * (N / 2) > 256)
         return fail(S2C_ERR_UNSUPPORTED, "fused integration: unsupported grouping");
@@ -264,6 +268,7 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
   }
   if (integral)
     return fail(S2C_ERR_UNSUPPORTED, "fused ReLU + integration needs the small-bandwidth path");
+  if (mask) return fail(S2C_ERR_UNSUPPORTED, "masked synthesis needs the small-bandwidth path");
   if (use_plane_kernels(N)) {
     HalfPanelsDev hp;
     hp.nbeta = N; hp.nl = K; hp.K = K; hp.npairs = pan.npairs;
@@ -568,6 +573,15 @@ int s2c_so3_rifft(const float* x, float* out, long nbatch, int b_in, int b_out, 
   if (bias && nfeature < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft: nfeature must be >= 1 with a bias");
   return so3_synthesis((const float2*)x, out, 1, 0, nbatch, b_in, b_out, for_grad != 0, kSo3Real,
                        bias, nfeature, ws, ws_bytes, as_stream(stream));
+}
+
+int s2c_so3_rifft_relu_grad(const float* x, const float* act, float* out, long nbatch, int b_in,
+                            int b_out, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !act || !out || nbatch < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rifft_relu_grad: bad argument");
+  return so3_synthesis((const float2*)x, out, 1, 0, nbatch, b_in, b_out, true, kSo3Real, nullptr, 0,
+                       nullptr, 0, as_stream(stream), nullptr, nullptr, act);
 }
 
 int s2c_so3_rifft_relu_integrate(const float* x, float* out, long nbatch, int b_in, int b_out,

@@ -54,6 +54,9 @@ struct InvFusedParams {
   // (so3_integrate(relu(.)), s2cnn/soft/so3_integrate.py:7-29) and write one number per batch element
   const float* iw;     // quadrature weights [N] (null: write the signal)
   float* isum;         // [nbatch]
+  // optional: a signal of the output's shape (unit stride); output samples where it is <= 0 are
+  // written as 0 - the gradient of a ReLU that was applied while this signal was read
+  const float* mask;
 };
 
 S2C_D float2 s2_product_entry(const InvFusedParams& p, int l, int m, int n, int i, int j) {
@@ -353,13 +356,29 @@ struct so3_inv_fused_impl {
               constexpr int p0 = fft_reg_pos<N>(g), p1 = fft_reg_pos<N>(g + 1);
               if constexpr (V == 4) {
                 constexpr int p2 = fft_reg_pos<N>(g + 2), p3 = fft_reg_pos<N>(g + 3);
-                *reinterpret_cast<float4*>(p.out + row1 + g) =
-                    make_float4(v[p0].x + add, v[p1].x + add, v[p2].x + add, v[p3].x + add);
-                *reinterpret_cast<float4*>(p.out + row2 + g) =
-                    make_float4(v[p0].y + add, v[p1].y + add, v[p2].y + add, v[p3].y + add);
+                float4 o1 = make_float4(v[p0].x + add, v[p1].x + add, v[p2].x + add, v[p3].x + add);
+                float4 o2 = make_float4(v[p0].y + add, v[p1].y + add, v[p2].y + add, v[p3].y + add);
+                if (p.mask) {
+                  const float4 k1 = *reinterpret_cast<const float4*>(p.mask + row1 + g);
+                  const float4 k2 = *reinterpret_cast<const float4*>(p.mask + row2 + g);
+                  o1 = make_float4(k1.x > 0.f ? o1.x : 0.f, k1.y > 0.f ? o1.y : 0.f,
+                                   k1.z > 0.f ? o1.z : 0.f, k1.w > 0.f ? o1.w : 0.f);
+                  o2 = make_float4(k2.x > 0.f ? o2.x : 0.f, k2.y > 0.f ? o2.y : 0.f,
+                                   k2.z > 0.f ? o2.z : 0.f, k2.w > 0.f ? o2.w : 0.f);
+                }
+                *reinterpret_cast<float4*>(p.out + row1 + g) = o1;
+                *reinterpret_cast<float4*>(p.out + row2 + g) = o2;
               } else {
-                *reinterpret_cast<float2*>(p.out + row1 + g) = make_float2(v[p0].x + add, v[p1].x + add);
-                *reinterpret_cast<float2*>(p.out + row2 + g) = make_float2(v[p0].y + add, v[p1].y + add);
+                float2 o1 = make_float2(v[p0].x + add, v[p1].x + add);
+                float2 o2 = make_float2(v[p0].y + add, v[p1].y + add);
+                if (p.mask) {
+                  const float2 k1 = *reinterpret_cast<const float2*>(p.mask + row1 + g);
+                  const float2 k2 = *reinterpret_cast<const float2*>(p.mask + row2 + g);
+                  o1 = make_float2(k1.x > 0.f ? o1.x : 0.f, k1.y > 0.f ? o1.y : 0.f);
+                  o2 = make_float2(k2.x > 0.f ? o2.x : 0.f, k2.y > 0.f ? o2.y : 0.f);
+                }
+                *reinterpret_cast<float2*>(p.out + row1 + g) = o1;
+                *reinterpret_cast<float2*>(p.out + row2 + g) = o2;
               }
             });
           } else {

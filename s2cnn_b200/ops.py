@@ -138,6 +138,24 @@ class Ops:
         self._log_new_tables("so3_rifft b %d -> %d" % (b_in, b_out))
         return out.view(*lead, n, n, n)
 
+    def so3_rifft_relu_grad(self, x, act):
+        """Gradient of ``so3_rfft(relu(act))`` with respect to ``act`` given the gradient ``x`` of the
+        spectrum: ``so3_rifft(x, for_grad=True)`` where ``act > 0``, else 0, in one kernel
+        (2 b <= 32).  x [nspec(b_in), ..., 2], act [..., 2b, 2b, 2b] -> like act."""
+        self._prep(x, act)
+        b_in = bandwidth_from_so3_nspec(x.size(0))
+        b_out = act.size(-1) // 2
+        lead = tuple(act.shape[:-3])
+        nbatch = _prod(lead)
+        assert tuple(x.shape[1:-1]) == lead and x.size(-1) == 2
+        x = x.contiguous()
+        act = act.contiguous()
+        out = torch.empty_like(act)
+        with self._ctx(x):
+            self.lib.call("s2c_so3_rifft_relu_grad", x.data_ptr(), act.data_ptr(), out.data_ptr(),
+                          nbatch, b_in, b_out, self._stream(x))
+        return out
+
     def so3_rifft_relu_integrate(self, x, bias=None, b_out=None):
         """so3_integrate(relu(so3_rifft(x) + bias)) in one kernel, the signal never written:
         [nspec(b_in), ..., 2] -> [...].  Only 2 b_out <= 32."""

@@ -74,8 +74,8 @@ class SO3_fft_real_relu(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):  # pylint: disable=W
         (x,) = ctx.saved_tensors
-        g = so3_rifft(grad_output.contiguous(), for_grad=True, b_out=ctx.b_in)
-        return torch.ops.aten.threshold_backward(g, x, 0), None   # g where x > 0, one pass
+        # the synthesis kernel writes 0 where x <= 0: no separate pass over the gradient signal
+        return cuda_ops().so3_rifft_relu_grad(grad_output.contiguous(), x), None
 
 
 class SO3_ifft_real(torch.autograd.Function):

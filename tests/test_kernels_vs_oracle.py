@@ -315,6 +315,24 @@ def test_rfft_with_relu_on_load(backend):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_spec,b_sig,lead", [(4, 6, (5,)), (6, 6, (2, 3)), (3, 5, (1,)), (10, 16, (2,))])
+def test_relu_on_load_gradient_in_the_synthesis_kernel(backend, b_spec, b_sig, lead):
+    """Backward of so3_rfft(relu(a), b_out = b_spec): the for_grad synthesis of the spectrum's
+    gradient with the ReLU mask applied while storing, against the oracle's two steps (the backward
+    of SO3_fft_real, s2cnn/soft/so3_fft.py:453-456, then the mask); a sample of ``a`` that is exactly
+    0 gets no gradient (torch's convention for relu)."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(31 + b_spec)
+    a = torch.randn(*lead, 2 * b_sig, 2 * b_sig, 2 * b_sig, generator=gen)
+    a.view(-1)[::7] = 0.0
+    g = torch.randn(n3(b_spec), *lead, 2, generator=gen)
+    want = O.so3_rifft(g, True, b_sig) * (a > 0)
+    got = ops.so3_rifft_relu_grad(g.to(dev), a.to(dev))
+    assert_close(got, want, "masked synthesis")
+    assert torch.all(got.cpu()[a <= 0] == 0)
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b_in,b_out,lead", [(6, 6, (5, 3)), (4, 7, (2, 2)), (5, 3, (7,)), (10, 10, (1, 2))])
 def test_synthesis_relu_integrate_fused(backend, b_in, b_out, lead):
     """so3_integrate(relu(so3_rifft(x) + bias)) in the synthesis kernel (the signal is never
