@@ -629,8 +629,9 @@ def strong_scaling(device, world, rank, net, flush, steps, batches_per_step, lan
     return {"workload": "net_b30_10_6, global batch 256 split over the ranks",
             "batch_per_gpu": b, "ms_per_batch": ms, "samples_per_s": BATCH_PER_GPU / (ms * 1e-3),
             "passes_in_flight": lanes,
-            "limiter": "launch latency and partly filled SMs: at %d samples per GPU the five "
-                       "kernels of a pass have fewer blocks than the GPU has SM slots" % b}
+            "limiter": "at %d samples per GPU the kernels of one pass have fewer blocks than the "
+                       "GPU has SM slots and launch latency shows; several passes in flight "
+                       "(passes_in_flight) fill the SMs" % b}
 
 
 # ------------------------------------------------------------------------------------------------
