@@ -1172,6 +1172,7 @@ static int static_load_tables(StaticDeviceState& st, int b_beta, int K, bool wei
   st.pan.data_g = nullptr;
   st.pan.g_bg = 0;
   st.pan.g_stride = 0;
+  st.pan.order = nullptr;
   st.pan.off = (const long long*)(st.tables + o_off);
   st.pan.data = (const float*)(st.tables + o_dat);
   st.b_beta = b_beta;

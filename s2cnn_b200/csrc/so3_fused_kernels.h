@@ -113,13 +113,31 @@ struct so3_inv_fused_impl {
     else fast = fast && (p.x_zstride % 2 == 0);
     if (fast) {
       const int pi = prod ? (int)(z0 / p.s2_fout) : 0, pj = prod ? (int)(z0 - (long)pi * p.s2_fout) : 0;
-      for (int r = ctx.tid; r < p.nrows; r += ctx.nthr) {
+      // With the product fused, the loads of the two S2 spectra are the cost of this loop.  The
+      // first one is the same small slice (its batch index is fixed) for every row: it is staged in
+      // the shared memory that the planes use later.  For the second one the threads walk the rows
+      // sorted by (l, n, m), so that the lanes of a warp mostly read the same address.
+      float2* xs_s = planes;
+      const int nlm = K * K;
+      const bool stage_xs = prod && (size_t)nlm * p.s2_fin <= (size_t)ZG * p.BG * plane_sz;
+      if (stage_xs) {
+        for (int e = ctx.tid; e < nlm * p.s2_fin; e += ctx.nthr) {
+          const int lm = e / p.s2_fin, k = e - lm * p.s2_fin;
+          xs_s[e] = p.xs[((long)lm * p.s2_nb + pi) * p.s2_fin + k];
+        }
+        ctx.sync();
+      }
+      const int* order = prod ? p.pan.order : nullptr;
+      for (int ri = ctx.tid; ri < p.nrows; ri += ctx.nthr) {
+        const int r = order ? order[ri] : ri;
         int l, m, n;
         rowmap_unpack(p.pan.rowmap[r], l, m, n);
         float2 av[ZG], bv[ZG];
         if (prod) {
-          const float2* xa = p.xs + ((long)(l * l + l + m) * p.s2_nb + pi) * p.s2_fin;
-          const float2* xb = p.xs + ((long)(l * l + l - m) * p.s2_nb + pi) * p.s2_fin;
+          const float2* xa = stage_xs ? xs_s + (l * l + l + m) * p.s2_fin
+                                      : p.xs + ((long)(l * l + l + m) * p.s2_nb + pi) * p.s2_fin;
+          const float2* xb = stage_xs ? xs_s + (l * l + l - m) * p.s2_fin
+                                      : p.xs + ((long)(l * l + l - m) * p.s2_nb + pi) * p.s2_fin;
           const float2* ya = p.ys + (long)(l * l + l + n) * p.s2_fin * p.s2_fout + pj;
           const float2* yb = p.ys + (long)(l * l + l - n) * p.s2_fin * p.s2_fout + pj;
 #pragma unroll

@@ -15,6 +15,7 @@
 // first call for a new (bandwidth, kind, device) therefore allocates and copies synchronously.
 #pragma once
 
+#include <algorithm>
 #include <cstdio>
 #include <map>
 #include <memory>
@@ -51,6 +52,10 @@ struct PanelsDev {
   const float* data_g;
   int g_bg;                 // betas per group
   int g_stride;             // floats per group slice (multiple of 4)
+  // Single-kernel path only (else null): the panel rows sorted by (l, n, m).  Threads that walk the
+  // rows in this order find the same (l, n) in neighbouring lanes (same address of the second S2
+  // spectrum when the product s2_mm is computed on the fly).
+  const int* order;
 };
 
 // ---- configuration of the single-kernel path (shared by the table builder and the kernels) ----
@@ -306,7 +311,20 @@ class TableCache {
       pd.data_g = nullptr;
       pd.g_bg = 0;
       pd.g_stride = 0;
+      pd.order = nullptr;
       if (!s2 && 2 * b_beta <= kFusedMaxN) {
+        std::vector<int> order(rowmap.size());
+        for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
+        auto key_of = [&](int r) {   // l, then n, then m
+          const int v = rowmap[(size_t)r];
+          return ((v & 0xff) << 16) | (((v >> 16) & 0xff) << 8) | ((v >> 8) & 0xff);
+        };
+        std::sort(order.begin(), order.end(), [&](int a, int b) { return key_of(a) < key_of(b); });
+        void* dord = dev_alloc(order.size() * sizeof(int));
+        if (!dord) return fail(S2C_ERR_CUDA, "table allocation failed");
+        rc = dev_upload(dord, order.data(), order.size() * sizeof(int));
+        if (rc) return rc;
+        pd.order = (const int*)dord;
         const int nbeta = 2 * b_beta, bg = fused_bg(nbeta), nrows = (int)rowmap.size();
         const int stride = (nrows * bg + 3) / 4 * 4;
         std::vector<float> grouped((size_t)stride * (nbeta / bg), 0.f);
@@ -429,6 +447,7 @@ class TableCache {
       dev_free((void*)kv.second.data);
       dev_free((void*)kv.second.off);
       dev_free((void*)kv.second.rowmap);
+      if (kv.second.order) dev_free((void*)kv.second.order);
       if (kv.second.data_g) dev_free((void*)kv.second.data_g);
     }
     for (auto& kv : quad_) dev_free((void*)kv.second);
