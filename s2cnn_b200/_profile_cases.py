@@ -7,6 +7,8 @@ within a minute (inputs above the 126 MB L2 where DRAM figures matter, a few hun
 
     inv10   so3_rifft, b = 10, 5120 signals          (kernel so3_inv_fused<20>)
     fwd10   so3_rfft,  b = 10 -> 6, 5120 signals     (kernel so3_fwd_fused<20>)
+    inv16   so3_rifft, b = 16, 1600 signals          (kernel so3_inv_fused<32>, 512-thread blocks)
+    fwd16   so3_rfft,  b = 16, 1600 signals          (kernel so3_fwd_fused<32>, 512-thread blocks)
     relay10 s2_mm + so3_rifft (b = 10) + bias + ReLU + so3_rfft (-> b = 6), batch 256, 1 -> 20
             features = 5120 signals                  (kernel so3_relay_fused<20>)
     mm      so3_mm, nl = 6, batch 256, 20 -> 40      (kernel so3_mm_tc_kernel)
@@ -33,6 +35,14 @@ def main(which):
         x = torch.randn(5120, 20, 20, 20, device=dev)
         for _ in range(3):
             ops.so3_rfft(x, b_out=6)
+    elif which == "inv16":
+        s = torch.randn(so3_nspec(16), 1600, 2, device=dev)
+        for _ in range(3):
+            ops.so3_rifft(s)
+    elif which == "fwd16":
+        x = torch.randn(1600, 32, 32, 32, device=dev)
+        for _ in range(3):
+            ops.so3_rfft(x)
     elif which == "relay10":
         xs = torch.randn(100, 256, 1, 2, device=dev)
         ys = torch.randn(100, 1, 20, 2, device=dev)

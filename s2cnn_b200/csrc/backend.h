@@ -200,6 +200,24 @@ __device__ __forceinline__ void bulk_load_issue(void* dst, const void* src, unsi
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// 32-byte global accesses (one full sector per lane and instruction); p must be 32-byte aligned
+struct float8 {
+  float4 lo, hi;
+};
+__device__ __forceinline__ float8 ld_global_256(const float* p) {
+  float8 r;
+  asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(r.lo.x), "=f"(r.lo.y), "=f"(r.lo.z), "=f"(r.lo.w), "=f"(r.hi.x), "=f"(r.hi.y),
+                 "=f"(r.hi.z), "=f"(r.hi.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_global_256(float* p, const float8& v) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "f"(v.lo.x), "f"(v.lo.y),
+               "f"(v.lo.z), "f"(v.lo.w), "f"(v.hi.x), "f"(v.hi.y), "f"(v.hi.z), "f"(v.hi.w)
+               : "memory");
+}
+
 __device__ __forceinline__ bool bulk_wait(const Ctx&, unsigned long long* bar, unsigned parity) {
   const unsigned addr = smem_u32(bar);
   for (int spin = 0; spin < (1 << 20); ++spin) {
@@ -378,6 +396,19 @@ namespace s2c {
 inline void bulk_barrier_init(unsigned long long*) {}
 inline void bulk_load_issue(void* dst, const void* src, unsigned bytes, unsigned long long*) {
   std::memcpy(dst, src, bytes);
+}
+struct float8 {
+  float4 lo, hi;
+};
+inline float8 ld_global_256(const float* p) {
+  float8 r;
+  r.lo = *reinterpret_cast<const float4*>(p);
+  r.hi = *reinterpret_cast<const float4*>(p + 4);
+  return r;
+}
+inline void st_global_256(float* p, const float8& v) {
+  *reinterpret_cast<float4*>(p) = v.lo;
+  *reinterpret_cast<float4*>(p + 4) = v.hi;
 }
 inline bool bulk_wait(const Ctx& ctx, unsigned long long*, unsigned) {
   ctx.sync();

@@ -57,6 +57,7 @@ struct InvFusedParams {
   // optional: a signal of the output's shape (unit stride); output samples where it is <= 0 are
   // written as 0 - the gradient of a ReLU that was applied while this signal was read
   const float* mask;
+  int wide;            // out (and mask) are 32-byte aligned and N % 8 == 0: 32-byte stores
 };
 
 S2C_D float2 s2_product_entry(const InvFusedParams& p, int l, int m, int n, int i, int j) {
@@ -128,6 +129,7 @@ struct so3_inv_fused_impl {
         ctx.sync();
       }
       const int* order = prod ? p.pan.order : nullptr;
+      const bool wide_x = !prod && p.x_zstride % 4 == 0 && reinterpret_cast<unsigned long long>(p.x) % 32 == 0;
       for (int ri = ctx.tid; ri < p.nrows; ri += ctx.nthr) {
         const int r = order ? order[ri] : ri;
         int l, m, n;
@@ -165,9 +167,18 @@ struct so3_inv_fused_impl {
             }
           }
         } else {
-          const float4* pa = reinterpret_cast<const float4*>(p.x + so3_row(l, m, n) * p.x_zstride + z0);
-          const float4* pb = reinterpret_cast<const float4*>(p.x + so3_row(l, -m, -n) * p.x_zstride + z0);
-          const float4 a01 = pa[0], a23 = pa[1], b01 = pb[0], b23 = pb[1];
+          const float2* qa = p.x + so3_row(l, m, n) * p.x_zstride + z0;
+          const float2* qb = p.x + so3_row(l, -m, -n) * p.x_zstride + z0;
+          float4 a01, a23, b01, b23;
+          if (wide_x) {   // the four batch elements of a row are one aligned 32-byte sector
+            const float8 a = ld_global_256(reinterpret_cast<const float*>(qa));
+            const float8 b = ld_global_256(reinterpret_cast<const float*>(qb));
+            a01 = a.lo; a23 = a.hi; b01 = b.lo; b23 = b.hi;
+          } else {
+            const float4* pa = reinterpret_cast<const float4*>(qa);
+            const float4* pb = reinterpret_cast<const float4*>(qb);
+            a01 = pa[0]; a23 = pa[1]; b01 = pb[0]; b23 = pb[1];
+          }
           av[0] = make_float2(a01.x, a01.y); av[1] = make_float2(a01.z, a01.w);
           av[2] = make_float2(a23.x, a23.y); av[3] = make_float2(a23.z, a23.w);
           bv[0] = make_float2(b01.x, b01.y); bv[1] = make_float2(b01.z, b01.w);
@@ -367,7 +378,33 @@ struct so3_inv_fused_impl {
         if (z < zc) {
           const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;   // first float of row ap
           const long row2 = row1 + (long)(N / 2) * N;
-          if (p.out_stride == 1) {
+          if (N % 8 == 0 && p.wide) {
+            // a row is a whole number of 32-byte sectors: one sector per store instruction (with
+            // 16-byte stores every sector would reach L2 in two halves)
+            auto keep = [](float4 v, float4 k) {
+              return make_float4(k.x > 0.f ? v.x : 0.f, k.y > 0.f ? v.y : 0.f, k.z > 0.f ? v.z : 0.f,
+                                 k.w > 0.f ? v.w : 0.f);
+            };
+            static_for<0, N / 8>([&](auto ic) {
+              constexpr int g = 8 * decltype(ic)::value;
+              float8 o1, o2;
+              o1.lo = make_float4(v[fft_reg_pos<N>(g)].x + add, v[fft_reg_pos<N>(g + 1)].x + add,
+                                  v[fft_reg_pos<N>(g + 2)].x + add, v[fft_reg_pos<N>(g + 3)].x + add);
+              o1.hi = make_float4(v[fft_reg_pos<N>(g + 4)].x + add, v[fft_reg_pos<N>(g + 5)].x + add,
+                                  v[fft_reg_pos<N>(g + 6)].x + add, v[fft_reg_pos<N>(g + 7)].x + add);
+              o2.lo = make_float4(v[fft_reg_pos<N>(g)].y + add, v[fft_reg_pos<N>(g + 1)].y + add,
+                                  v[fft_reg_pos<N>(g + 2)].y + add, v[fft_reg_pos<N>(g + 3)].y + add);
+              o2.hi = make_float4(v[fft_reg_pos<N>(g + 4)].y + add, v[fft_reg_pos<N>(g + 5)].y + add,
+                                  v[fft_reg_pos<N>(g + 6)].y + add, v[fft_reg_pos<N>(g + 7)].y + add);
+              if (p.mask) {
+                const float8 k1 = ld_global_256(p.mask + row1 + g), k2 = ld_global_256(p.mask + row2 + g);
+                o1.lo = keep(o1.lo, k1.lo); o1.hi = keep(o1.hi, k1.hi);
+                o2.lo = keep(o2.lo, k2.lo); o2.hi = keep(o2.hi, k2.hi);
+              }
+              st_global_256(p.out + row1 + g, o1);
+              st_global_256(p.out + row2 + g, o2);
+            });
+          } else if (p.out_stride == 1) {
             constexpr int V = (N % 4 == 0) ? 4 : 2;
             static_for<0, N / V>([&](auto ic) {
               constexpr int g = V * decltype(ic)::value;
@@ -437,6 +474,7 @@ struct FwdFusedParams {
   PanelsDev pan;       // beta grid of b_in, nl = b_out, K
   const float2* tw;
   int nbatch, K, BG, KP, PS, nrows, mode, relu;
+  int wide;            // x is 32-byte aligned, unit stride and N % 8 == 0: 32-byte loads
 };
 
 template <int N>
@@ -468,7 +506,20 @@ struct so3_fwd_fused_impl {
         if (z < zc) {
           const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;
           const long row2 = row1 + (long)(N / 2) * N;
-          if (p.in_stride == 1) {
+          if (N % 8 == 0 && p.wide) {
+            static_for<0, N / 8>([&](auto ic) {   // one 32-byte sector per load instruction
+              constexpr int g = 8 * decltype(ic)::value;
+              const float8 a = ld_global_256(p.x + row1 + g), b = ld_global_256(p.x + row2 + g);
+              v[g] = make_float2(a.lo.x, b.lo.x);
+              v[g + 1] = make_float2(a.lo.y, b.lo.y);
+              v[g + 2] = make_float2(a.lo.z, b.lo.z);
+              v[g + 3] = make_float2(a.lo.w, b.lo.w);
+              v[g + 4] = make_float2(a.hi.x, b.hi.x);
+              v[g + 5] = make_float2(a.hi.y, b.hi.y);
+              v[g + 6] = make_float2(a.hi.z, b.hi.z);
+              v[g + 7] = make_float2(a.hi.w, b.hi.w);
+            });
+          } else if (p.in_stride == 1) {
             constexpr int V = (N % 4 == 0) ? 4 : 2;
             static_for<0, N / V>([&](auto ic) {
               constexpr int g = V * decltype(ic)::value;
