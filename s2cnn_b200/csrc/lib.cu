@@ -128,7 +128,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     f.pan = pan; f.tw = fft.tw;
     f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N); f.PS = fused_plane_stride(N, K);
     f.nrows = pan.nrows; f.mode = mode; f.relu = relu;
-    f.wide = in_stride == 1 && in_off == 0 && N % 8 == 0 && (uintptr_t)x % 32 == 0;
+    f.wide = in_stride == 1 && in_off == 0 && N % 4 == 0 && (uintptr_t)x % 32 == 0;
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
     const size_t sm = fwd_fused_smem_bytes(N, pan.nrows);
@@ -249,7 +249,7 @@ static int so3_synthesis(const float2* x, float* out, long out_stride, long out_
     f.mask = mask;
     if (mask && (out_stride != 1 || out_off != 0))
       return fail(S2C_ERR_UNSUPPORTED, "masked synthesis: real output only");
-    f.wide = out_stride == 1 && out_off == 0 && N % 8 == 0 && out && (uintptr_t)out % 32 == 0 &&
+    f.wide = out_stride == 1 && out_off == 0 && N % 4 == 0 && out && (uintptr_t)out % 32 == 0 &&
              (uintptr_t)mask % 32 == 0;
     if (integral) {
       if (N % f.BG != 0 || kFusedZG * f.BG * (N / 2) > 256)

@@ -40,7 +40,10 @@ inline size_t s2_gradx_thin_smem(int nl, int fi, int fo) {
 // block = (l, m, tile of kThinRows batch rows); thread = (row, slice of n)
 S2C_KERNEL(s2_mm_gradx_thin, S2ThinParams) {
   const int tiles_i = (p.nb + kThinRows - 1) / kThinRows;
-  const int lm = ctx.bid / tiles_i, itile = ctx.bid - lm * tiles_i;
+  // largest degrees first: a block's work grows with 2l + 1, and the blocks that start last should
+  // be the short ones
+  const int rbid = ctx.nblk - 1 - ctx.bid;
+  const int lm = rbid / tiles_i, itile = rbid - lm * tiles_i;
   const int l = thin_isqrt(lm), m = lm - l * l;
   const int L = 2 * l + 1;
   float2* ys = reinterpret_cast<float2*>(smem);                     // [L][fi][fo]
@@ -105,7 +108,8 @@ inline size_t s2_grady_thin_smem(int fo) {
 
 // block = (l, n); thread = (slice of the batch rows, j); all of (m, i) is summed inside the block
 S2C_KERNEL_BOUNDS(s2_mm_grady_thin, S2ThinParams, 1024, 1) {
-  const int l = thin_isqrt(ctx.bid), n = ctx.bid - l * l;
+  const int rbid = ctx.nblk - 1 - ctx.bid;     // largest degrees (the long blocks) first
+  const int l = thin_isqrt(rbid), n = rbid - l * l;
   const int L = 2 * l + 1;
   const int nsl = ctx.nthr / p.fo;
   const int j = ctx.tid % p.fo, sl = ctx.tid / p.fo;

@@ -57,7 +57,7 @@ struct InvFusedParams {
   // optional: a signal of the output's shape (unit stride); output samples where it is <= 0 are
   // written as 0 - the gradient of a ReLU that was applied while this signal was read
   const float* mask;
-  int wide;            // out (and mask) are 32-byte aligned and N % 8 == 0: 32-byte stores
+  int wide;            // out (and mask) are 32-byte aligned and N % 4 == 0: 32-byte stores
 };
 
 S2C_D float2 s2_product_entry(const InvFusedParams& p, int l, int m, int n, int i, int j) {
@@ -378,24 +378,38 @@ struct so3_inv_fused_impl {
         if (z < zc) {
           const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;   // first float of row ap
           const long row2 = row1 + (long)(N / 2) * N;
-          if (N % 8 == 0 && p.wide) {
-            // a row is a whole number of 32-byte sectors: one sector per store instruction (with
-            // 16-byte stores every sector would reach L2 in two halves)
-            auto keep = [](float4 v, float4 k) {
-              return make_float4(k.x > 0.f ? v.x : 0.f, k.y > 0.f ? v.y : 0.f, k.z > 0.f ? v.z : 0.f,
-                                 k.w > 0.f ? v.w : 0.f);
+          if (N % 4 == 0 && p.wide) {
+            // 32-byte stores, one whole sector per lane and instruction (with 16-byte stores every
+            // sector would reach L2 in two halves).  Rows of N % 8 == 4 floats start on a sector
+            // boundary only every other row (the planes themselves do, 4 N^2 bytes apart): even
+            // rows end, odd rows begin with a 16-byte piece.
+            auto keep = [](float4 val, float4 k) {
+              return make_float4(k.x > 0.f ? val.x : 0.f, k.y > 0.f ? val.y : 0.f,
+                                 k.z > 0.f ? val.z : 0.f, k.w > 0.f ? val.w : 0.f);
             };
-            static_for<0, N / 8>([&](auto ic) {
-              constexpr int g = 8 * decltype(ic)::value;
+            auto quad = [&](auto gc, float4& o1, float4& o2) {
+              constexpr int g = decltype(gc)::value;
+              constexpr int p0 = fft_reg_pos<N>(g), p1 = fft_reg_pos<N>(g + 1);
+              constexpr int p2 = fft_reg_pos<N>(g + 2), p3 = fft_reg_pos<N>(g + 3);
+              o1 = make_float4(v[p0].x + add, v[p1].x + add, v[p2].x + add, v[p3].x + add);
+              o2 = make_float4(v[p0].y + add, v[p1].y + add, v[p2].y + add, v[p3].y + add);
+            };
+            auto st4 = [&](auto gc) {
+              constexpr int g = decltype(gc)::value;
+              float4 o1, o2;
+              quad(gc, o1, o2);
+              if (p.mask) {
+                o1 = keep(o1, *reinterpret_cast<const float4*>(p.mask + row1 + g));
+                o2 = keep(o2, *reinterpret_cast<const float4*>(p.mask + row2 + g));
+              }
+              *reinterpret_cast<float4*>(p.out + row1 + g) = o1;
+              *reinterpret_cast<float4*>(p.out + row2 + g) = o2;
+            };
+            auto st8 = [&](auto gc) {
+              constexpr int g = decltype(gc)::value;
               float8 o1, o2;
-              o1.lo = make_float4(v[fft_reg_pos<N>(g)].x + add, v[fft_reg_pos<N>(g + 1)].x + add,
-                                  v[fft_reg_pos<N>(g + 2)].x + add, v[fft_reg_pos<N>(g + 3)].x + add);
-              o1.hi = make_float4(v[fft_reg_pos<N>(g + 4)].x + add, v[fft_reg_pos<N>(g + 5)].x + add,
-                                  v[fft_reg_pos<N>(g + 6)].x + add, v[fft_reg_pos<N>(g + 7)].x + add);
-              o2.lo = make_float4(v[fft_reg_pos<N>(g)].y + add, v[fft_reg_pos<N>(g + 1)].y + add,
-                                  v[fft_reg_pos<N>(g + 2)].y + add, v[fft_reg_pos<N>(g + 3)].y + add);
-              o2.hi = make_float4(v[fft_reg_pos<N>(g + 4)].y + add, v[fft_reg_pos<N>(g + 5)].y + add,
-                                  v[fft_reg_pos<N>(g + 6)].y + add, v[fft_reg_pos<N>(g + 7)].y + add);
+              quad(gc, o1.lo, o2.lo);
+              quad(std::integral_constant<int, g + 4>{}, o1.hi, o2.hi);
               if (p.mask) {
                 const float8 k1 = ld_global_256(p.mask + row1 + g), k2 = ld_global_256(p.mask + row2 + g);
                 o1.lo = keep(o1.lo, k1.lo); o1.hi = keep(o1.hi, k1.hi);
@@ -403,7 +417,16 @@ struct so3_inv_fused_impl {
               }
               st_global_256(p.out + row1 + g, o1);
               st_global_256(p.out + row2 + g, o2);
-            });
+            };
+            if constexpr (N % 8 == 0) {
+              static_for<0, N / 8>([&](auto ic) { st8(std::integral_constant<int, 8 * decltype(ic)::value>{}); });
+            } else if (ap & 1) {
+              st4(std::integral_constant<int, 0>{});
+              static_for<0, N / 8>([&](auto ic) { st8(std::integral_constant<int, 4 + 8 * decltype(ic)::value>{}); });
+            } else {
+              static_for<0, N / 8>([&](auto ic) { st8(std::integral_constant<int, 8 * decltype(ic)::value>{}); });
+              st4(std::integral_constant<int, N - 4>{});
+            }
           } else if (p.out_stride == 1) {
             constexpr int V = (N % 4 == 0) ? 4 : 2;
             static_for<0, N / V>([&](auto ic) {
@@ -474,7 +497,7 @@ struct FwdFusedParams {
   PanelsDev pan;       // beta grid of b_in, nl = b_out, K
   const float2* tw;
   int nbatch, K, BG, KP, PS, nrows, mode, relu;
-  int wide;            // x is 32-byte aligned, unit stride and N % 8 == 0: 32-byte loads
+  int wide;            // x is 32-byte aligned, unit stride and N % 4 == 0: 32-byte loads
 };
 
 template <int N>
@@ -506,9 +529,20 @@ struct so3_fwd_fused_impl {
         if (z < zc) {
           const long row1 = (((z0 + z) * N + bg0 + bi) * (long)N + ap) * N;
           const long row2 = row1 + (long)(N / 2) * N;
-          if (N % 8 == 0 && p.wide) {
-            static_for<0, N / 8>([&](auto ic) {   // one 32-byte sector per load instruction
-              constexpr int g = 8 * decltype(ic)::value;
+          if (N % 4 == 0 && p.wide) {
+            // 32-byte loads, one whole sector per lane and instruction; rows of N % 8 == 4 floats
+            // start on a sector boundary only every other row (see the synthesis kernel)
+            auto ld4 = [&](auto gc) {
+              constexpr int g = decltype(gc)::value;
+              const float4 a = *reinterpret_cast<const float4*>(p.x + row1 + g);
+              const float4 b = *reinterpret_cast<const float4*>(p.x + row2 + g);
+              v[g] = make_float2(a.x, b.x);
+              v[g + 1] = make_float2(a.y, b.y);
+              v[g + 2] = make_float2(a.z, b.z);
+              v[g + 3] = make_float2(a.w, b.w);
+            };
+            auto ld8 = [&](auto gc) {
+              constexpr int g = decltype(gc)::value;
               const float8 a = ld_global_256(p.x + row1 + g), b = ld_global_256(p.x + row2 + g);
               v[g] = make_float2(a.lo.x, b.lo.x);
               v[g + 1] = make_float2(a.lo.y, b.lo.y);
@@ -518,7 +552,16 @@ struct so3_fwd_fused_impl {
               v[g + 5] = make_float2(a.hi.y, b.hi.y);
               v[g + 6] = make_float2(a.hi.z, b.hi.z);
               v[g + 7] = make_float2(a.hi.w, b.hi.w);
-            });
+            };
+            if constexpr (N % 8 == 0) {
+              static_for<0, N / 8>([&](auto ic) { ld8(std::integral_constant<int, 8 * decltype(ic)::value>{}); });
+            } else if (ap & 1) {
+              ld4(std::integral_constant<int, 0>{});
+              static_for<0, N / 8>([&](auto ic) { ld8(std::integral_constant<int, 4 + 8 * decltype(ic)::value>{}); });
+            } else {
+              static_for<0, N / 8>([&](auto ic) { ld8(std::integral_constant<int, 8 * decltype(ic)::value>{}); });
+              ld4(std::integral_constant<int, N - 4>{});
+            }
           } else if (p.in_stride == 1) {
             constexpr int V = (N % 4 == 0) ? 4 : 2;
             static_for<0, N / V>([&](auto ic) {
