@@ -92,6 +92,14 @@ int s2c_so3_rfft(const float* x, float* out, long nbatch, int b_in, int b_out, i
  * "unsupported". */
 int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_out,
                       void* workspace, size_t workspace_bytes, void* stream);
+/* s2c_so3_rfft plus one by-product: sums [nbatch] = the plain sum of every signal over its (2b)^3
+ * samples (read off the (m, n) = (0, 0) bins inside the kernel).  With x the gradient of a layer's
+ * output this is what the gradient of the bias added at s2cnn/soft/s2_conv.py:45 / so3_conv.py:56
+ * needs (summed over the batch by the caller), without another pass over the largest tensor of the
+ * step.  Only for 2 b_in <= 32 (single-kernel path); other sizes return status 4 ("unsupported")
+ * and write nothing. */
+int s2c_so3_rfft_sums(const float* x, float* out, float* sums, long nbatch, int b_in, int b_out,
+                      int for_grad, void* stream);
 /* x [nbatch, 2b_in, 2b_in, 2b_in, 2] complex -> out [nspec(b_out), nbatch, 2].
  * Replaces so3_fft, s2cnn/soft/so3_fft.py:12-61. */
 int s2c_so3_fft(const float* x, float* out, long nbatch, int b_in, int b_out, int for_grad,

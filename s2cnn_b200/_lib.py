@@ -40,6 +40,7 @@ _SIGNATURES = {
     "s2c_so3_fft_workspace_min": (c_size_t, [c_int, c_int]),
     "s2c_so3_rfft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
     "s2c_so3_rfft_relu": (c_int, [_P, _P, c_long, c_int, c_int, _P, c_size_t, _P]),
+    "s2c_so3_rfft_sums": (c_int, [_P, _P, _P, c_long, c_int, c_int, c_int, _P]),
     "s2c_debug_force_general_path": (None, [c_int]),
     "s2c_debug_plane_chunk": (None, [c_int]),
     "s2c_so3_fft": (c_int, [_P, _P, c_long, c_int, c_int, c_int, _P, c_size_t, _P]),
@@ -111,6 +112,16 @@ class Lib:
             rc = getattr(self.cdll, name)(*args)
         if rc != 0:
             raise S2cError("%s failed (status %d): %s" % (name, rc, self.last_error()))
+
+    def try_call(self, name, *args):
+        """Like ``call`` for entry points that answer status 4 ("unsupported", nothing written) for
+        sizes outside their fast path: returns False then, True on success, raises otherwise."""
+        rc = getattr(self.cdll, name)(*args)
+        if rc == 4:
+            return False
+        if rc != 0:
+            raise S2cError("%s failed (status %d): %s" % (name, rc, self.last_error()))
+        return True
 
     def __getattr__(self, name):
         return getattr(self.cdll, name)

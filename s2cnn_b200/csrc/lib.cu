@@ -112,7 +112,7 @@ static int check_b(int b_in, int b_out) {
 // ---------------------------------------------------------------------------------------------
 static int so3_analysis(const float* x, long in_stride, long in_off, float2* out, long nbatch,
                         int b_in, int b_out, bool weighted, int mode, void* ws, size_t ws_bytes,
-                        stream_t st, bool relu = false) {
+                        stream_t st, bool relu = false, float* sums = nullptr) {
   const int N = 2 * b_in, K = std::min(b_in, b_out);
   FftDev fft;
   PanelsDev pan;
@@ -129,6 +129,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     f.nbatch = (int)nbatch; f.K = K; f.BG = fused_bg(N); f.KP = fused_kp(N); f.PS = fused_plane_stride(N, K);
     f.nrows = pan.nrows; f.mode = mode; f.relu = relu;
     f.wide = in_stride == 1 && in_off == 0 && N % 4 == 0 && (uintptr_t)x % 32 == 0;
+    f.sums = sums;
     int rc = S2C_OK;
     const long grid = (nbatch + kFusedZG - 1) / kFusedZG;
     const size_t sm = fwd_fused_smem_bytes(N, pan.nrows);
@@ -137,6 +138,7 @@ static int so3_analysis(const float* x, long in_stride, long in_off, float2* out
     return rc;
   }
   if (relu) return fail(S2C_ERR_UNSUPPORTED, "fused ReLU input needs the small-bandwidth path");
+  if (sums) return fail(S2C_ERR_UNSUPPORTED, "per-signal sums need the small-bandwidth path");
   if (use_plane_kernels(N)) {
     HalfPanelsDev hp;
     hp.nbeta = N; hp.nl = b_out; hp.K = K; hp.npairs = pan.npairs;
@@ -553,6 +555,15 @@ int s2c_so3_rfft_relu(const float* x, float* out, long nbatch, int b_in, int b_o
   if (!x || !out || nbatch < 1) return fail(S2C_ERR_BAD_ARG, "s2c_so3_rfft_relu: bad argument");
   return so3_analysis(x, 1, 0, (float2*)out, nbatch, b_in, b_out, true, kSo3Real, ws, ws_bytes,
                       as_stream(stream), true);
+}
+
+int s2c_so3_rfft_sums(const float* x, float* out, float* sums, long nbatch, int b_in, int b_out,
+                      int for_grad, void* stream) {
+  S2C_TRY(check_b(b_in, b_out));
+  if (!x || !out || !sums || nbatch < 1)
+    return fail(S2C_ERR_BAD_ARG, "s2c_so3_rfft_sums: bad argument");
+  return so3_analysis(x, 1, 0, (float2*)out, nbatch, b_in, b_out, !for_grad, kSo3Real, nullptr, 0,
+                      as_stream(stream), false, sums);
 }
 
 void s2c_debug_force_general_path(int level) { g_force_general = level < 0 ? 0 : level; }

@@ -498,6 +498,10 @@ struct FwdFusedParams {
   const float2* tw;
   int nbatch, K, BG, KP, PS, nrows, mode, relu;
   int wide;            // x is 32-byte aligned, unit stride and N % 4 == 0: 32-byte loads
+  // optional by-product [nbatch]: the plain sum of every signal over its (2b)^3 samples (the
+  // (m, n) = (0, 0) bin of each beta plane, summed over beta) - what the gradient of a bias that
+  // was added to the signal needs, without another pass over the signal
+  float* sums;
 };
 
 template <int N>
@@ -514,6 +518,7 @@ struct so3_fwd_fused_impl {
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
     for (int it = ctx.tid; it < p.nrows * ZG; it += ctx.nthr) acc[it] = make_float2(0.f, 0.f);
     ctx.sync();
+    float zsum = 0.f;   // threads 0 .. ZG-1: running sum of their batch element's (0, 0) bins
 
     for (int bg0 = 0; bg0 < N; bg0 += p.BG) {
       const int bc = (N - bg0) < p.BG ? (N - bg0) : p.BG;
@@ -626,6 +631,8 @@ struct so3_fwd_fused_impl {
         });
       }
       ctx.sync();
+      if (p.sums && ctx.tid < ZG)
+        for (int bi = 0; bi < bc; ++bi) zsum += planes[(size_t)(ctx.tid * p.BG + bi) * plane_sz].x;
       // ---- accumulate the Wigner contraction over the betas of this group: one panel row
       //      (l, m, n) per thread, all ZG batch elements -----------------------------------------
       if (p.BG == 4 && N % 4 == 0) {
@@ -691,6 +698,7 @@ struct so3_fwd_fused_impl {
       }
       ctx.sync();
     }
+    if (p.sums && ctx.tid < zc) p.sums[z0 + ctx.tid] = zsum;
     // ---- write the spectrum and its Hermitian mirror ----------------------------------------
     for (int it = ctx.tid; it < p.nrows * ZG; it += ctx.nthr) {
       const int r = it / ZG, z = it - r * ZG;

@@ -94,6 +94,28 @@ class Ops:
         self._log_new_tables("so3_rfft b %d -> %d" % (b_in, b_out))
         return out.view(-1, *lead, 2)
 
+    def so3_rfft_with_sums(self, x, for_grad=False, b_out=None):
+        """``so3_rfft(x)`` and, as a by-product of the same kernel, the plain sum of every signal
+        over its samples ([...] like the leading dimensions of x).  Sizes outside the single-kernel
+        path (2 b_in > 32) take two passes."""
+        self._prep(x)
+        b_in = x.size(-1) // 2
+        b_out = b_in if b_out is None else b_out
+        lead = tuple(x.shape[:-3])
+        nbatch = _prod(lead)
+        x = x.contiguous()
+        if 2 * b_in <= 32:
+            out = x.new_empty((so3_nspec(b_out), nbatch, 2))
+            sums = x.new_empty((nbatch,))
+            with self._ctx(x):
+                ok = self.lib.try_call("s2c_so3_rfft_sums", x.data_ptr(), out.data_ptr(),
+                                       sums.data_ptr(), nbatch, b_in, b_out, int(bool(for_grad)),
+                                       self._stream(x))
+            if ok:
+                self._log_new_tables("so3_rfft b %d -> %d" % (b_in, b_out))
+                return out.view(-1, *lead, 2), sums.view(lead)
+        return self.so3_rfft(x, for_grad=for_grad, b_out=b_out), x.sum(dim=(-3, -2, -1))
+
     def so3_fft(self, x, for_grad=False, b_out=None):
         """[..., 2b, 2b, 2b, 2] complex -> [nspec(b_out), ..., 2]"""
         self._prep(x)

@@ -32,12 +32,17 @@ class _S2ProductSynthesis(torch.autograd.Function):
         gx = gy = gb = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             b = round(x.size(0) ** 0.5)
-            gz = so3_rfft(grad_output, for_grad=True, b_out=b)  # [l * m * n, batch, f_out, complex]
+            if ctx.needs_input_grad[2] and grad_output.dim() == 5:
+                # the bias gradient is a by-product of the analysis kernel (per-signal sums)
+                gz, sums = cuda_ops().so3_rfft_with_sums(grad_output, for_grad=True, b_out=b)
+                gb = sums.sum(dim=0).reshape(ctx.bias_shape)
+            else:
+                gz = so3_rfft(grad_output, for_grad=True, b_out=b)  # [l * m * n, batch, f_out, complex]
             if ctx.needs_input_grad[0]:
                 gx = cuda_ops().s2_mm_gradx(gz, y, x.size(1), x.size(2))
             if ctx.needs_input_grad[1]:
                 gy = cuda_ops().s2_mm_grady(gz, x, y.size(2))
-        if ctx.needs_input_grad[2]:
+        if ctx.needs_input_grad[2] and gb is None:
             gb = grad_output.sum(dim=(0, 2, 3, 4)).reshape(ctx.bias_shape)
         return gx, gy, gb
 

@@ -104,6 +104,10 @@ class SO3_ifft_real_bias(torch.autograd.Function):
     def backward(ctx, grad_output):  # pylint: disable=W
         grad_output = grad_output.contiguous()
         gx = gb = None
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and grad_output.dim() == 5:
+            # the bias gradient is a by-product of the analysis kernel (per-signal sums)
+            gx, sums = cuda_ops().so3_rfft_with_sums(grad_output, for_grad=True, b_out=ctx.b_in)
+            return gx, sums.sum(dim=0).reshape(ctx.bias_shape)
         if ctx.needs_input_grad[0]:
             gx = so3_rfft(grad_output, for_grad=True, b_out=ctx.b_in)
         if ctx.needs_input_grad[1]:

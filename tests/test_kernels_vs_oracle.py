@@ -315,6 +315,21 @@ def test_rfft_with_relu_on_load(backend):
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
+@pytest.mark.parametrize("b_in,b_out,lead", [(6, 6, (3, 2)), (5, 3, (7,)), (16, 16, (2, 3)), (17, 5, (2,))])
+def test_rfft_with_per_signal_sums(backend, b_in, b_out, lead):
+    """The analysis kernel's by-product (the plain sum of every signal, used for the gradient of
+    the bias added at s2cnn/soft/s2_conv.py:45) next to the spectrum itself; 2b = 34 takes the
+    two-pass fallback."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(77 + b_in)
+    x = torch.randn(*lead, 2 * b_in, 2 * b_in, 2 * b_in, generator=gen) + 0.3
+    spec, sums = ops.so3_rfft_with_sums(x.to(dev), for_grad=True, b_out=b_out)
+    assert_close(spec, O.so3_rfft(x, True, b_out), "spectrum")
+    assert tuple(sums.shape) == tuple(lead)
+    assert_close(sums, x.double().sum(dim=(-3, -2, -1)).float(), "per-signal sums")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
 @pytest.mark.parametrize("b_spec,b_sig,lead", [(4, 6, (5,)), (6, 6, (2, 3)), (3, 5, (1,)), (10, 16, (2,))])
 def test_relu_on_load_gradient_in_the_synthesis_kernel(backend, b_spec, b_sig, lead):
     """Backward of so3_rfft(relu(a), b_out = b_spec): the for_grad synthesis of the spectrum's
