@@ -348,7 +348,8 @@ def test_relu_on_load_gradient_in_the_synthesis_kernel(backend, b_spec, b_sig, l
 
 
 @pytest.mark.parametrize("backend", backends.BACKENDS)
-@pytest.mark.parametrize("b_in,b_out,lead", [(6, 6, (5, 3)), (4, 7, (2, 2)), (5, 3, (7,)), (10, 10, (1, 2))])
+@pytest.mark.parametrize("b_in,b_out,lead", [(6, 6, (5, 3)), (4, 7, (2, 2)), (5, 3, (7,)), (10, 10, (1, 2)),
+                                             (16, 16, (3,))])   # 512-thread blocks
 def test_synthesis_relu_integrate_fused(backend, b_in, b_out, lead):
     """so3_integrate(relu(so3_rifft(x) + bias)) in the synthesis kernel (the signal is never
     written), incl. a batch count that leaves a partial block."""
