@@ -294,6 +294,21 @@ struct so3_fwd_wigner_r_impl {
 #endif
     for (int t = 0; t < kRowsDepth - 1; ++t) rows_issue<N, 2>(ring, t, pn.a, pn.b, L, lane);
 
+    // This lane's output in every step: value lane = r * 16 + s * 8 + z * 2 + c of the transpose-
+    // reduce, i.e. degree lmin + li + r, frequency +-m, batch element z, real / imaginary part.
+    // Its spectrum row and the Hermitian mirror row advance by two degrees per step; with
+    // row(l, m, n) = l (4 l^2 - 1) / 3 + (l + m)(2 l + 1) + l + n the step is a quadratic in l, kept
+    // by differences (no multiplications or divisions in the loop).
+    const int o_r = lane >> 4, o_s = (lane >> 3) & 1, o_z = (lane >> 1) & 3, o_c = lane & 1;
+    const int o_mm = o_s ? -m : m;
+    const bool o_ok = zbase + o_z < zc && !(self && o_s == 1);
+    const float o_fudge = ((o_mm - n) & 1) ? -1.f : 1.f;
+    float* const o_base = reinterpret_cast<float*>(p.out + zbase + o_z) + o_c;
+    const long o_zs2 = 2 * p.out_zstride;
+    int o_row1 = (int)so3_row(lmin + o_r, o_mm, n), o_row2 = (int)so3_row(lmin + o_r, -o_mm, -n);
+    int o_d1 = 8 * (lmin + o_r) * (lmin + o_r) + 24 * (lmin + o_r) + 22 + 4 * o_mm;
+    int o_d2 = o_d1 - 8 * o_mm, o_dd = 32 * (lmin + o_r) + 80;
+
     float va[2][JL], vb[2][JL];     // rows li, li + 1 of the two half panels
     for (int li = 0; li < Lloop; li += 2) {
       rows_wait_oldest();
@@ -335,23 +350,23 @@ struct so3_fwd_wigner_r_impl {
       }
       const float mine = rows_reduce32(ctx, val, lane, xch);   // value `lane` summed over the warp
       const float other = rows_partner(ctx, mine, lane, xch);  // the other component of the number
-      // lane = r * 16 + s * 8 + z * 2 + c
-      const int r = lane >> 4, s = (lane >> 3) & 1, z = (lane >> 1) & 3, c = lane & 1;
-      const int l = lmin + li + r, zz = zbase + z;
-      if (li + r < L && zz < zc && !(self && s == 1)) {
-        const int mm = s ? -m : m;
-        float* o1 = reinterpret_cast<float*>(p.out + so3_row(l, mm, n) * p.out_zstride + zz) + c;
-        const float fudge = ((mm - n) & 1) ? -1.f : 1.f;
+      if (li + o_r < L && o_ok) {
+        float* o1 = o_base + o_row1 * o_zs2;
         const bool mirror = n > 0;      // for n = 0 the mirror (-m, 0) is computed directly
-        float* o2 = reinterpret_cast<float*>(p.out + so3_row(l, -mm, -n) * p.out_zstride + zz) + c;
+        float* o2 = o_base + o_row2 * o_zs2;
         if (p.mode == kSo3Real) {
           *o1 = mine;
-          if (mirror) *o2 = c ? -fudge * mine : fudge * mine;
+          if (mirror) *o2 = o_c ? -o_fudge * mine : o_fudge * mine;
         } else {   // += i * (re + i im):  re -= im, im += re;   mirror += i * fudge * conj
-          *o1 += c ? other : -other;
-          if (mirror) *o2 += fudge * other;
+          *o1 += o_c ? other : -other;
+          if (mirror) *o2 += o_fudge * other;
         }
       }
+      o_row1 += o_d1;
+      o_row2 += o_d2;
+      o_d1 += o_dd;
+      o_d2 += o_dd;
+      o_dd += 64;
     }
   }
 };
