@@ -13,6 +13,8 @@ this is the minimal layer the path needs on an 8-GPU NVSwitch box:
 The real-space ``kernel.grad`` ([f_in, f_out, n_grid]) is what gets reduced, not the ~14x larger
 spectral gradient: the kernel transform is linear, so the two orders commute.
 """
+import datetime
+
 import torch
 import torch.distributed as dist
 
@@ -156,14 +158,27 @@ class GradientReducer:
         self._pending[bi] -= 1
         self._launch_ready()
 
-    def finish(self):
+    def finish(self, timeout_s=None):
         """Launches the remaining buckets, waits for all of them and returns the number of
-        elements reduced."""
+        elements reduced.  With ``timeout_s`` the host waits at most that long for each bucket and
+        raises ``TimeoutError`` if a peer never joined its all-reduce (failure detection on the
+        host: nothing on the GPU is made to fault; the process group is unusable afterwards and the
+        caller is expected to tear the job down)."""
         if not _active():
             return 0
         self._launch_ready(force=True)
-        for w in self._works:
-            w.wait()
+        for i, w in enumerate(self._works):
+            if timeout_s is None:
+                w.wait()
+                continue
+            try:
+                done = w.wait(datetime.timedelta(seconds=float(timeout_s)))
+            except RuntimeError as e:     # gloo and NCCL both raise on an expired wait
+                raise TimeoutError("gradient all-reduce %d of %d did not complete within %.1f s: %s"
+                                   % (i + 1, len(self._works), timeout_s, e)) from e
+            if done is False:
+                raise TimeoutError("gradient all-reduce %d of %d did not complete within %.1f s"
+                                   % (i + 1, len(self._works), timeout_s))
         self._works = []
         if self.average:
             world = dist.get_world_size(self.group)

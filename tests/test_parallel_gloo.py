@@ -132,3 +132,55 @@ def test_two_ranks_match_single_process(tmp_path):
             assert_close(a, b, "overlapped reducer, rank %d" % rank)
         for a, b in zip(out["red2"], out["red2_ref"]):
             assert_close(a, b, "overlapped reducer with an idle rank, rank %d" % rank)
+
+
+def _timeout_worker(rank, world, port, tmp):
+    """Rank 1 never reaches its all-reduce; rank 0 must get a TimeoutError out of finish() instead
+    of waiting for ever.  Both leave without touching the (now unusable) process group again."""
+    sys.path.insert(0, HERE)
+    import backends
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=__import__("datetime").timedelta(seconds=60))
+    import s2cnn_b200 as S
+    from s2cnn_b200 import parallel
+    with backends.active("emul"):
+        torch.manual_seed(1)
+        grid = S.so3_near_identity_grid(max_beta=0.4, n_alpha=4, n_beta=1, n_gamma=2)
+        conv = S.SO3Convolution(2, 2, 3, 2, grid)
+        red = parallel.GradientReducer(conv)
+        red.zero_grad()
+        result = "no finish"
+        if rank == 0:
+            conv(torch.randn(2, 2, 6, 6, 6)).sum().backward()   # the hook launches the all-reduce
+            try:
+                red.finish(timeout_s=2.0)
+                result = "returned"
+            except TimeoutError:
+                result = "timeout"
+        else:
+            import time
+            time.sleep(6.0)       # well past rank 0's limit; never joins the collective
+        with open(os.path.join(tmp, "timeout%d.txt" % rank), "w") as f:
+            f.write(result)
+    os._exit(0)
+
+
+def test_finish_times_out_when_a_rank_never_joins(tmp_path):
+    sys.path.insert(0, HERE)
+    import emul
+    emul.build()
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_timeout_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()       # exactly the processes started here
+    assert not alive, "a rank hung instead of timing out"
+    assert open(os.path.join(str(tmp_path), "timeout0.txt")).read() == "timeout"
+    assert open(os.path.join(str(tmp_path), "timeout1.txt")).read() == "no finish"
