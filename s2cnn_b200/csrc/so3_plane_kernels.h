@@ -137,6 +137,19 @@ struct so3_fwd_plane_impl {
     };
     float2 vnext[8];
     load_batch(0, vnext);
+#ifndef S2C_EMUL
+    // Ask L2 for the plane that a block starting about one wave later will read (blocks are
+    // dispatched in index order, two per SM): its first rows then arrive with the latency of L2
+    // instead of HBM.  The register prefetch above reaches only one batch of rows ahead.
+    if (p.in_stride == 1) {
+      const long ahead = ctx.bid + 2L * 148;
+      if (ahead < ctx.nblk) {
+        const float* nx = p.x + p.in_off + ahead * (long)N * N;
+        for (int i = ctx.tid * 32; i < N * N; i += ctx.nthr * 32)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(nx + i));
+      }
+    }
+#endif
     for (int i = ctx.tid; i < N; i += ctx.nthr) tw[i] = p.tw[i];
     ctx.sync();
 #pragma unroll
