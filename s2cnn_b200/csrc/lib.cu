@@ -641,6 +641,7 @@ static int relay_launch(const float2* x, const float2* xs, const float2* ys, int
   f.BG = relay_bg(N, b_in, f.pin.nrows, f.pout.nrows);
   if (f.BG < 1) return fail(S2C_ERR_UNSUPPORTED, std::string(who) + ": shared memory");
   S2C_TRY(TableCache::get().grouped(b_mid, b_in, b_in, false, f.BG, &f.win_g, &f.win_stride));
+  S2C_TRY(TableCache::get().grouped(b_mid, b_next, b_next, true, f.BG, &f.wout_g, &f.wout_stride));
   f.x = x; f.x_zstride = nz;
   f.xs = xs; f.ys = ys;
   f.s2_nb = s2_nb; f.s2_fin = s2_fin; f.s2_fout = nfeat;

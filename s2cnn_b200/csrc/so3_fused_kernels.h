@@ -639,12 +639,17 @@ struct so3_fwd_fused_impl {
         // four betas per group: the row's four table values are one 16-byte load, fetched (with the
         // row's indices) one pass ahead of their use so that the latency of global memory overlaps
         // the multiply-adds of the pass before
+        // (from the copy of the table regrouped by beta group when there is one: neighbouring rows
+        // are then neighbouring 16-byte pieces, whole sectors per warp)
+        const bool grouped = p.pan.data_g != nullptr && p.pan.g_bg == 4;
+        const float* wbase = grouped ? p.pan.data_g + (size_t)(bg0 / 4) * p.pan.g_stride : p.pan.data + bg0;
+        const int wstep = grouped ? 4 : N;
         int r = ctx.tid;
         int packed = 0;
         float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < p.nrows) {
           packed = p.pan.rowmap[r];
-          w4 = *reinterpret_cast<const float4*>(p.pan.data + (long)r * N + bg0);
+          w4 = *reinterpret_cast<const float4*>(wbase + (long)r * wstep);
         }
         while (r < p.nrows) {
           const int rn = r + ctx.nthr;
@@ -652,7 +657,7 @@ struct so3_fwd_fused_impl {
           float4 w4n = make_float4(0.f, 0.f, 0.f, 0.f);
           if (rn < p.nrows) {
             packed_n = p.pan.rowmap[rn];
-            w4n = *reinterpret_cast<const float4*>(p.pan.data + (long)rn * N + bg0);
+            w4n = *reinterpret_cast<const float4*>(wbase + (long)rn * wstep);
           }
           int l, m, n;
           rowmap_unpack(packed, l, m, n);
@@ -679,7 +684,9 @@ struct so3_fwd_fused_impl {
       for (int r = ctx.tid; r < p.nrows; r += ctx.nthr) {
         int l, m, n;
         rowmap_unpack(p.pan.rowmap[r], l, m, n);
-        const float* w = p.pan.data + (long)r * N + bg0;
+        const float* w = (p.pan.data_g != nullptr && p.pan.g_bg == p.BG)
+                             ? p.pan.data_g + (size_t)(bg0 / p.BG) * p.pan.g_stride + (size_t)r * p.BG
+                             : p.pan.data + (long)r * N + bg0;
         const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
         float2 a[ZG];
 #pragma unroll

@@ -35,6 +35,8 @@ struct RelayParams {
   int win_stride;
   // analysis side
   PanelsDev pout;      // beta grid of b, nl = b_next, K = Kout (weighted)
+  const float* wout_g; // pout's values regrouped for groups of BG betas
+  int wout_stride;
   float2* out;         // spectrum rows of out_zstride complex
   long out_zstride;
   const float2* tw;
@@ -350,7 +352,8 @@ struct so3_relay_fused_impl {
       for (int r = ctx.tid; r < nrows_out; r += ctx.nthr) {
         int l, m, n;
         rowmap_unpack(p.pout.rowmap[r], l, m, n);
-        const float* w = p.pout.data + (long)r * N + bg0;
+        // the group's table values of neighbouring rows are neighbouring pieces of the regrouped copy
+        const float* w = p.wout_g + (size_t)grp * p.wout_stride + (size_t)r * p.BG;
         const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
         float2 a[ZG];
 #pragma unroll
