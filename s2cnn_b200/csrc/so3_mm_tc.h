@@ -600,7 +600,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
               make_float2(v[2 * c2], v[2 * c2 + 1]);
       }
     } else if (r < M) {
-      if constexpr (VEC) {
+      if (VEC && nsplit == 1 && CW % 8 == 0 && reinterpret_cast<unsigned long long>(p.c) % 32 == 0) {
+        // a lane owns a row: 32-byte stores write whole sectors (16-byte ones would send every
+        // sector to L2 in two halves); CW % 8 == 0 keeps a group of 8 inside one outer column index
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          const int gcol = col0 + cbase + 8 * c8;
+          if (gcol < Np) {
+            const int co = gcol / CW, rem = gcol - co * CW;
+            float* dst = p.c + ((spec0 + (long)ro * sro + (long)co * sco) * RI + ri) * CW + rem;
+            float8 o;
+            o.lo = make_float4(v[8 * c8], v[8 * c8 + 1], v[8 * c8 + 2], v[8 * c8 + 3]);
+            o.hi = make_float4(v[8 * c8 + 4], v[8 * c8 + 5], v[8 * c8 + 6], v[8 * c8 + 7]);
+            st_global_256(dst, o);
+          }
+        }
+      } else if constexpr (VEC) {
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
           const int gcol = col0 + cbase + 4 * c4;
