@@ -510,7 +510,13 @@ struct so3_fwd_fused_impl {
     constexpr int ZG = kFusedZG;
     const int K = p.K, KP = p.KP;
     float2* tw = reinterpret_cast<float2*>(smem);
-    float2* acc = tw + N;                               // [nrows][ZG]
+    // accumulated spectrum, split in two arrays of 16-byte rows: [nrows][z 0, 1] then [nrows][z 2, 3]
+    // (threads that own neighbouring rows then read and write neighbouring 16-byte pieces; with 32
+    // contiguous bytes per row the 8-byte accesses of a warp fell four to a bank)
+    float2* acc = tw + N;
+    static_assert(kFusedZG == 4, "split accumulator layout");
+    auto acc_at = [&](int r, int z) -> float2& { return acc[((z >> 1) * p.nrows + r) * 2 + (z & 1)]; };
+    float4* acc4 = reinterpret_cast<float4*>(acc);       // acc4[r] = z 0, 1;  acc4[nrows + r] = z 2, 3
     float2* planes = acc + (size_t)p.nrows * ZG;        // [ZG * BG][N][KP]
     const int plane_sz = p.PS;
     const long z0 = (long)ctx.bid * ZG;
@@ -663,9 +669,9 @@ struct so3_fwd_fused_impl {
           rowmap_unpack(packed, l, m, n);
           const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
           const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
-          float2 a[ZG];
-#pragma unroll
-          for (int z = 0; z < ZG; ++z) a[z] = acc[r * ZG + z];
+          const float4 a01 = acc4[r], a23 = acc4[p.nrows + r];
+          float2 a[ZG] = {make_float2(a01.x, a01.y), make_float2(a01.z, a01.w),
+                          make_float2(a23.x, a23.y), make_float2(a23.z, a23.w)};
 #pragma unroll
           for (int bi = 0; bi < 4; ++bi)
 #pragma unroll
@@ -674,8 +680,8 @@ struct so3_fwd_fused_impl {
               a[z].x = fmaf(wv[bi], xv.x, a[z].x);
               a[z].y = fmaf(wv[bi], xv.y, a[z].y);
             }
-#pragma unroll
-          for (int z = 0; z < ZG; ++z) acc[r * ZG + z] = a[z];
+          acc4[r] = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
+          acc4[p.nrows + r] = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
           r = rn;
           packed = packed_n;
           w4 = w4n;
@@ -688,9 +694,9 @@ struct so3_fwd_fused_impl {
                              ? p.pan.data_g + (size_t)(bg0 / p.BG) * p.pan.g_stride + (size_t)r * p.BG
                              : p.pan.data + (long)r * N + bg0;
         const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
-        float2 a[ZG];
-#pragma unroll
-        for (int z = 0; z < ZG; ++z) a[z] = acc[r * ZG + z];
+        const float4 a01 = acc4[r], a23 = acc4[p.nrows + r];
+        float2 a[ZG] = {make_float2(a01.x, a01.y), make_float2(a01.z, a01.w),
+                        make_float2(a23.x, a23.y), make_float2(a23.z, a23.w)};
         for (int bi = 0; bi < bc; ++bi) {
           const float wv = w[bi];
 #pragma unroll
@@ -700,8 +706,8 @@ struct so3_fwd_fused_impl {
             a[z].y = fmaf(wv, xv.y, a[z].y);
           }
         }
-#pragma unroll
-        for (int z = 0; z < ZG; ++z) acc[r * ZG + z] = a[z];
+        acc4[r] = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
+        acc4[p.nrows + r] = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
       }
       ctx.sync();
     }
@@ -712,7 +718,7 @@ struct so3_fwd_fused_impl {
       if (z >= zc) continue;
       int l, m, n;
       rowmap_unpack(p.pan.rowmap[r], l, m, n);
-      const float2 a = acc[it];
+      const float2 a = acc_at(r, z);
       const float fudge = ((m - n) & 1) ? -1.f : 1.f;
       float2* o1 = p.out + so3_row(l, m, n) * p.out_zstride + z0 + z;
       float2* o2 = p.out + so3_row(l, -m, -n) * p.out_zstride + z0 + z;

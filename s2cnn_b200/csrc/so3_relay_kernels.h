@@ -67,7 +67,10 @@ struct so3_relay_fused_impl {
     int4* pinfo = reinterpret_cast<int4*>(Xh + (size_t)nrows_in * ZG);      // [npairs_in]
     float* Wg = reinterpret_cast<float*>(pinfo + p.pin.npairs);             // [nrows_in][BG]
     unsigned long long* wbar = reinterpret_cast<unsigned long long*>(Wg + p.win_stride);
-    float2* acc = reinterpret_cast<float2*>(wbar + 2);                      // [nrows_out][ZG]
+    // accumulated spectrum of the analysis, split like Xh: [nrows_out][z 0, 1] then [nrows_out][z 2, 3]
+    float2* acc = reinterpret_cast<float2*>(wbar + 2);
+    auto acc_at = [&](int r, int z) -> float2& { return acc[((z >> 1) * nrows_out + r) * 2 + (z & 1)]; };
+    float4* acc4 = reinterpret_cast<float4*>(acc);
     float2* planes = acc + (size_t)nrows_out * ZG;                          // [ZG * BG][N][KP]
     const unsigned wbytes = (unsigned)p.win_stride * sizeof(float);
     if (ctx.tid == 0) {
@@ -355,9 +358,9 @@ struct so3_relay_fused_impl {
         // the group's table values of neighbouring rows are neighbouring pieces of the regrouped copy
         const float* w = p.wout_g + (size_t)grp * p.wout_stride + (size_t)r * p.BG;
         const float2* src = planes + (m < 0 ? m + N : m) * KP + n;
-        float2 a[ZG];
-#pragma unroll
-        for (int z = 0; z < ZG; ++z) a[z] = acc[r * ZG + z];
+        const float4 a01 = acc4[r], a23 = acc4[nrows_out + r];
+        float2 a[ZG] = {make_float2(a01.x, a01.y), make_float2(a01.z, a01.w),
+                        make_float2(a23.x, a23.y), make_float2(a23.z, a23.w)};
         for (int bi = 0; bi < bc; ++bi) {
           const float wv = w[bi];
 #pragma unroll
@@ -367,8 +370,8 @@ struct so3_relay_fused_impl {
             a[z].y = fmaf(wv, xv.y, a[z].y);
           }
         }
-#pragma unroll
-        for (int z = 0; z < ZG; ++z) acc[r * ZG + z] = a[z];
+        acc4[r] = make_float4(a[0].x, a[0].y, a[1].x, a[1].y);
+        acc4[nrows_out + r] = make_float4(a[2].x, a[2].y, a[3].x, a[3].y);
       }
       ctx.sync();
     }
@@ -378,7 +381,7 @@ struct so3_relay_fused_impl {
       if (z >= zc) continue;
       int l, m, n;
       rowmap_unpack(p.pout.rowmap[r], l, m, n);
-      const float2 a = acc[it];
+      const float2 a = acc_at(r, z);
       const float fudge = ((m - n) & 1) ? -1.f : 1.f;
       p.out[so3_row(l, m, n) * p.out_zstride + z0 + z] = a;
       if (!(m == 0 && n == 0))
