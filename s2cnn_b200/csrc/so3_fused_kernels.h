@@ -80,7 +80,12 @@ struct so3_inv_fused_impl {
     constexpr int ZG = kFusedZG;
     const int K = p.K, KP = p.KP;
     float2* tw = reinterpret_cast<float2*>(smem);
-    float2* Xh = tw + N;                              // [nrows][ZG]
+    // half spectrum, split in two arrays of 16-byte rows: [nrows][z 0, 1] then [nrows][z 2, 3] (the
+    // rows of consecutive frequency pairs then start 16 L instead of 32 L bytes apart, which halves
+    // the bank conflicts of the per-pair 16-byte loads)
+    float2* Xh = tw + N;
+    static_assert(kFusedZG == 4, "split spectrum layout");
+    auto xh_at = [&](int r, int z) -> float2& { return Xh[((z >> 1) * p.nrows + r) * 2 + (z & 1)]; };
     int4* pinfo = reinterpret_cast<int4*>(Xh + (size_t)p.nrows * ZG);    // [npairs]
     float* Wg = reinterpret_cast<float*>(pinfo + p.pan.npairs);           // [nrows][BG] of one group
     unsigned long long* wbar = reinterpret_cast<unsigned long long*>(Wg + p.pan.g_stride);
@@ -192,7 +197,7 @@ struct so3_inv_fused_impl {
             a = make_float2(a.y, -a.x);
             b = make_float2(b.y, -b.x);
           }
-          Xh[r * ZG + z] = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
+          xh_at(r, z) = make_float2(0.5f * (a.x + fudge * b.x), 0.5f * (a.y - fudge * b.y));
         }
       }
     } else {
@@ -238,7 +243,7 @@ struct so3_inv_fused_impl {
           bv = make_float2(bv.y, -bv.x);
         }
         const float fudge = ((m - n) & 1) ? -1.f : 1.f;
-        Xh[it] = make_float2(0.5f * (av.x + fudge * bv.x), 0.5f * (av.y - fudge * bv.y));
+        xh_at(it / ZG, it % ZG) = make_float2(0.5f * (av.x + fudge * bv.x), 0.5f * (av.y - fudge * bv.y));
       }
     }
     }
@@ -259,14 +264,15 @@ struct so3_inv_fused_impl {
         for (int pr = ctx.tid; pr < p.pan.npairs; pr += ctx.nthr) {
           const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
           const float4* w4 = reinterpret_cast<const float4*>(wslice + info.x * 4);
-          const float4* x4 = reinterpret_cast<const float4*>(Xh + info.x * ZG);
+          const float4* xa4 = reinterpret_cast<const float4*>(Xh) + info.x;
+          const float4* xb4 = xa4 + p.nrows;
           float2 s[4][ZG];
 #pragma unroll
           for (int bi = 0; bi < 4; ++bi)
 #pragma unroll
             for (int z = 0; z < ZG; ++z) s[bi][z] = make_float2(0.f, 0.f);
           for (int li = 0; li < info.y; ++li) {
-            const float4 w = w4[li], xa = x4[2 * li], xb = x4[2 * li + 1];
+            const float4 w = w4[li], xa = xa4[li], xb = xb4[li];
             const float wv[4] = {w.x, w.y, w.z, w.w};
             const float2 xv[ZG] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w),
                                    make_float2(xb.x, xb.y), make_float2(xb.z, xb.w)};
@@ -294,7 +300,7 @@ struct so3_inv_fused_impl {
         const int pr = it / bc, bi = it - pr * bc;
         const int4 info = pinfo[pr];  // {first panel row, L, FFT row of m, n}
         const float* w = wslice + info.x * p.BG + bi;
-        const float2* xs = Xh + info.x * ZG;
+        const int xrow = info.x;
         float2 acc[ZG];
 #pragma unroll
         for (int z = 0; z < ZG; ++z) acc[z] = make_float2(0.f, 0.f);
@@ -302,7 +308,7 @@ struct so3_inv_fused_impl {
           const float wv = w[li * p.BG];
 #pragma unroll
           for (int z = 0; z < ZG; ++z) {
-            const float2 xv = xs[li * ZG + z];
+            const float2 xv = xh_at(xrow + li, z);
             acc[z].x = fmaf(wv, xv.x, acc[z].x);
             acc[z].y = fmaf(wv, xv.y, acc[z].y);
           }
