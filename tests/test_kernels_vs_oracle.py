@@ -476,3 +476,22 @@ def test_bandwidth_64_large_path_on_the_emulation_build():
     got = ops.so3_rfft(x, b_out=64)
     assert_close(got, ref, "b=64 rfft (emulation)")
     assert_close(ops.so3_rifft(got), O.so3_rifft(ref), "b=64 rifft (emulation)")
+
+
+@pytest.mark.parametrize("backend", backends.BACKENDS)
+def test_tensors_aligned_to_16_bytes_only(backend):
+    """Signals and spectra whose first element sits 16 bytes into an allocation (a view of a larger
+    buffer): the kernels' 32-byte accesses need 32-byte alignment and must not be used then."""
+    ops, dev = backends.get(backend)
+    gen = torch.Generator().manual_seed(5)
+    b = 8
+    n = 3 * (2 * b) ** 3
+    flat = torch.randn(n + 4, generator=gen).to(dev)
+    x = flat[4:].view(3, 2 * b, 2 * b, 2 * b)
+    assert x.data_ptr() % 32 == 16 or not x.is_cuda
+    spec = ops.so3_rfft(x)
+    assert_close(spec, O.so3_rfft(x.cpu()), "rfft of a 16-byte aligned view")
+    sflat = torch.randn(n3(b) * 4 * 2 + 4, generator=gen).to(dev)
+    s = sflat[4:].view(n3(b), 4, 2)
+    got = ops.so3_rifft(s)
+    assert_close(got, O.so3_rifft(s.cpu()), "rifft of a 16-byte aligned spectrum")
