@@ -486,19 +486,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
     // the cursor of the loads runs two K blocks ahead of the one being staged
     long cur_a = 0, cur_b = 0;
     int cur_kb = 0;
+    unsigned validA = 0, validB = 0;      // bit q: slot q has a source address at all
+#pragma unroll
+    for (int q = 0; q < kSlots; ++q) {
+      if (gA[q]) validA |= 1u << q;
+      if (gB[q]) validB |= 1u << q;
+    }
     auto prefetch = [&](float4 (&ra)[kSlots], float4 (&rb)[kSlots]) {
       const bool last = cur_kb + 1 == p.nblk;
+      if (!last) {
+        // a full block: every slot that has a source is loaded; the others hold the zeros they were
+        // given before the loop (or by the last block of the previous run)
+#pragma unroll
+        for (int q = 0; q < kSlots; ++q) {
+          if ((validA >> q) & 1u) ra[q] = load4(gA[q] + cur_a, a_str, a_st, false);
+          if ((validB >> q) & 1u) rb[q] = load4(gB[q] + cur_b, b_str, b_st, false);
+        }
+        ++cur_kb; cur_a += a_stepk; cur_b += b_stepk;
+        return;
+      }
 #pragma unroll
       for (int q = 0; q < kSlots; ++q) {
         ra[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gA[q] && (!last || ((tailA >> q) & 1u)))
-          ra[q] = load4(gA[q] + cur_a, a_str, a_st, last && ((tailA2 >> q) & 1u));
+        if (((validA & tailA) >> q) & 1u)
+          ra[q] = load4(gA[q] + cur_a, a_str, a_st, (tailA2 >> q) & 1u);
         rb[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gB[q] && (!last || ((tailB >> q) & 1u)))
-          rb[q] = load4(gB[q] + cur_b, b_str, b_st, last && ((tailB2 >> q) & 1u));
+        if (((validB & tailB) >> q) & 1u)
+          rb[q] = load4(gB[q] + cur_b, b_str, b_st, (tailB2 >> q) & 1u);
       }
-      if (last) { cur_kb = 0; cur_a += a_stepo; cur_b += b_stepo; }
-      else { ++cur_kb; cur_a += a_stepk; cur_b += b_stepk; }
+      cur_kb = 0; cur_a += a_stepo; cur_b += b_stepo;
     };
     // v = hi + lo with hi carrying the 10 explicit TF32 mantissa bits (the tensor core ignores the
     // lower 13 bits of its inputs, so lo = v - hi needs no further rounding)
@@ -550,6 +566,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) so3_mm_tc_kernel(const MmTcPara
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem_u32(&full[s])) : "memory");
       return true;
     };
+#pragma unroll
+    for (int q = 0; q < kSlots; ++q)
+      ra0[q] = rb0[q] = ra1[q] = rb1[q] = make_float4(0.f, 0.f, 0.f, 0.f);
     prefetch(ra0, rb0);
     if (nit > 1) prefetch(ra1, rb1);
     for (int it = 0; it < nit && !*abort_flag; it += 2) {
